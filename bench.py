@@ -1,0 +1,451 @@
+#!/usr/bin/env python
+"""Benchmark of the flash-GQA path.  Prints ONE JSON line on rank 0.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads (synthetic, seeded; shapes are the baseline configurations of this path):
+    decode_b60      GQA decode, B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D]   (default, headline)
+    decode_long     one sequence, S=1,048,576, Hq=64, Hkv=8, KV sharded by position across GPUs
+                    (all-gather of per-GPU partials + LSE combine; strong scaling)
+    prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
+    prefill_causal  prefill forward, causal, B=8 per... see --help; batch-sharded
+
+A step is one pass of the hot path over one batch.  `value` is whole-job throughput with inputs
+resident in HBM; `e2e` is the same metric through the package's public launcher with HOST buffers
+(pinned), host<->device copies inside the timed region.  `--impl reference` times upstream's own CPU
+implementation of the decode path on this machine's host cores instead.
+"""
+import argparse
+import json
+import os
+import re
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on the headline
+# workload, from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"decode_b60": None, "prefill_nc": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS,
+            "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t_begin, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        for ts, line in self.rows:
+            if ts < t_begin - 0.02 or ts > t_end + 0.06:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def decode_bytes(B, S, Hq, Hkv, D=128):
+    """Algorithmic bytes of one decode pass: K and V read once, Q read, O written (bf16)."""
+    return 2 * (B * S * Hkv * D) * 2 + 2 * (B * Hq * D) * 2
+
+
+def prefill_flops(B, Hq, Sq, Skv, D=128, causal=False):
+    f = 4.0 * B * Hq * Sq * Skv * D
+    return f / 2 if causal else f
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import cuda_llm_ops_b200 as ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks = measured_peaks()
+    wl = args.workload
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def randn_bf16(shape, std=1.0):
+        # generated in slices to keep the fp32 temporary small
+        out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        flat = out.view(-1)
+        step = 1 << 26
+        for i in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - i)
+            flat[i:i + n] = (torch.randn(n, generator=gen, device=dev) * std).to(torch.bfloat16)
+        return out
+
+    extra = {}
+    if wl == "decode_b60":
+        B, S, Hq, Hkv = 60, 4096, 128, 8
+        layout = ops.KV_BSHD if args.layout == "bshd" else ops.KV_BHSD
+        kshape = (B, S, Hkv, 128) if layout == ops.KV_BSHD else (B, Hkv, S, 128)
+        q, k, v = randn_bf16((B, Hq, 128)), randn_bf16(kshape), randn_bf16(kshape)
+        out = torch.empty_like(q)
+        step_fn = lambda: ops.gqa_decode(q, k, v, kv_layout=layout, out=out)  # noqa: E731
+        units_per_rank = decode_bytes(B, S, Hq, Hkv)
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
+        launches_per_step = 2
+        scaling = "weak"
+        config = {"workload": "decode_b60: GQA decode B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, one query token, "
+                              "K/V %s, N(0,1) seeded" % ("[B,S,Hkv,D]" if layout == ops.KV_BSHD else "[B,Hkv,S,D]"),
+                  "global_batch": B * world, "kv_seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "inputs (1.0 GB per GPU) exceed the 126 MB L2; no flush needed"}
+        host_in = [q, k, v]
+    elif wl == "decode_long":
+        S_total, Hq, Hkv = 1 << 20, 64, 8
+        s0, s1 = ops.shard_kv_positions(S_total, world, rank)
+        q = randn_bf16((1, Hq, 128), 0.5)
+        if world > 1:
+            dist.broadcast(q, 0)
+        k, v = randn_bf16((1, s1 - s0, Hkv, 128), 0.5), randn_bf16((1, s1 - s0, Hkv, 128), 0.5)
+        dec = ops.KVShardedDecoder() if world > 1 else None
+        part = torch.zeros((1, 1, Hq, 130), dtype=torch.float32, device=dev)
+        if world > 1:
+            step_fn = lambda: dec.decode(q, k, v, kv_layout=ops.KV_BSHD)  # noqa: E731
+            launches_per_step = 3
+        else:
+            out = torch.empty_like(q)
+            step_fn = lambda: ops.gqa_decode(q, k, v, kv_layout=ops.KV_BSHD, out=out)  # noqa: E731
+            launches_per_step = 2
+        total_units = decode_bytes(1, S_total, Hq, Hkv)
+        units_per_rank = decode_bytes(1, s1 - s0, Hq, Hkv)
+        metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
+        scaling = "strong"
+        config = {"workload": "decode_long: one sequence, S=1048576, Hq=64, Hkv=8, D=128, K/V [1,S,Hkv,D] 0.5*N(0,1)",
+                  "global_batch": 1, "kv_seq_len": S_total,
+                  "sharding": "KV positions; all-gather of (O,m,l) partials + LSE combine" if world > 1 else "none",
+                  "l2": "inputs exceed L2"}
+        host_in = [q, k, v]
+    elif wl in ("prefill_nc", "prefill_causal"):
+        causal = wl == "prefill_causal"
+        if causal:
+            B, S, Hq, Hkv = max(1, 8 // world), 16384, 64, 8
+            scaling = "strong"
+        else:
+            B, S, Hq, Hkv = 1, 4096, 16, 1
+            scaling = "weak"
+        q, k, v = randn_bf16((B, Hq, S, 128)), randn_bf16((B, Hkv, S, 128)), randn_bf16((B, Hkv, S, 128))
+        out = torch.empty_like(q)
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        step_fn = lambda: ops.launch_flash_gqa_forward_bf16_kernel(q, k, v, out=out, lse=lse, causal=causal)  # noqa: E731
+        units_per_rank = prefill_flops(B, Hq, S, S, causal=causal)
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "gqa_prefill_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 1
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if not causal else None
+        if flush is not None:
+            inner = step_fn
+            step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        config = {"workload": "%s: GQA prefill forward %s, B=%d per GPU, S=%d, Hq=%d, Hkv=%d, D=128, [B,H,S,D], N(0,1) seeded"
+                              % (wl, "causal" if causal else "non-causal", B, S, Hq, Hkv),
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (its time is subtracted; see kernel_ms)"
+                        if flush is not None else "inputs exceed L2"}
+        host_in = [q, k, v]
+    else:
+        raise SystemExit("unknown workload " + wl)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_fn()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    # per-step device times on the launching stream (torch's current stream is what the C ABI receives)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    flush_only = None
+    barrier()
+    t_begin = time.time()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    if wl == "prefill_nc":
+        for i in range(args.steps):
+            flush.zero_()
+            starts[i].record()
+            inner()
+            ends[i].record()
+    else:
+        for i in range(args.steps):
+            starts[i].record()
+            step_fn()
+            ends[i].record()
+    t1.record()
+    barrier()
+    t_end = time.time()
+    per_step = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    if wl == "prefill_nc":
+        total_ms = sum(per_step)  # the flush writes sit between the per-step brackets
+    else:
+        total_ms = t0.elapsed_time(t1)
+    # keep the GPU busy with the same kernel a little longer so that the clock samples see load
+    if rank == 0 and (t_end - t_begin) < 0.6:
+        reps = int(min(20000, 0.6 / max(total_ms / args.steps / 1e3, 1e-6)))
+        for _ in range(reps):
+            step_fn()
+        torch.cuda.synchronize()
+        t_end = time.time()
+        extra["clock_sampling"] = "timed region + %d untimed repeats of the same step" % reps
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+
+    tt = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    total_ms = float(tt.item())
+    ms_per_step = total_ms / args.steps
+    value = total_units / (ms_per_step * 1e-3) / scale_div
+
+    # ---- end to end: pinned host buffers -> device -> kernel -> host ----
+    e2e = None
+    if wl in ("decode_b60", "prefill_nc"):
+        host = [t.cpu().pin_memory() for t in host_in]
+        dev_in = [torch.empty_like(t) for t in host_in]
+        out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        if wl == "decode_b60":
+            def e2e_step():
+                for d, h in zip(dev_in, host):
+                    d.copy_(h, non_blocking=True)
+                ops.gqa_decode(dev_in[0], dev_in[1], dev_in[2], kv_layout=layout, out=out)
+                out_host.copy_(out, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        else:
+            def e2e_step():
+                for d, h in zip(dev_in, host):
+                    d.copy_(h, non_blocking=True)
+                ops.launch_flash_gqa_forward_bf16_kernel(dev_in[0], dev_in[1], dev_in[2], out=out, lse=lse, causal=False)
+                out_host.copy_(out, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        n_e2e = max(3, min(args.steps, 10))
+        e2e_step()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        et = torch.tensor([e0.elapsed_time(e1) / n_e2e], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(et, op=dist.ReduceOp.MAX)
+        e2e_ms = float(et.item())
+        e2e = {"value": total_units / (e2e_ms * 1e-3) / scale_div, "unit": unit, "ms_per_step": e2e_ms,
+               "steps": n_e2e,
+               "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in host)),
+               "d2h_bytes_per_step": int(out_host.numel() * out_host.element_size())}
+
+    rc, detail = ops.device_status()
+    if rc != 0:
+        raise SystemExit("device status %d %s" % (rc, detail))
+
+    if rank != 0:
+        return
+    kernel_ms = statistics.mean(per_step)
+    achieved = units_per_rank / (kernel_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+    peak = peaks["hbm_gbs"] if bound == "hbm" else peaks["bf16_tflops"]
+    traffic = NCU_TRAFFIC_BYTES.get(wl)
+    roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
+                "kernel": "decode_splitkv_kernel (+decode_merge_kernel in the same bracket)" if bound == "hbm"
+                          else "prefill_fwd_kernel",
+                "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
+    if bound == "hbm":
+        roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
+    else:
+        roofline["frac_of_nominal_2250TF"] = achieved / 2250.0
+        roofline["frac_of_sustained"] = achieved / peaks["bf16_tflops_sustained"]
+
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "roofline": roofline,
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "impl": "ours"}
+    line["us_per_step"] = ms_per_step * 1e3
+    if wl == "decode_b60" and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_decode()
+    if extra:
+        line["extra"] = extra
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arms (upstream's own CPU implementation of the decode path)
+# ------------------------------------------------------------------------------------------------
+def _run_ref_binary():
+    """One run of the unmodified upstream benchmark program (stubbed runtime): its CPU loop at the headline shape."""
+    import oracle_lib as ol
+    out = subprocess.run([ol.REF_BIN], capture_output=True, text=True, timeout=1200)
+    m = re.search(r"CPU time = ([0-9.eE+-]+)s", out.stdout)
+    if out.returncode != 0 or not m:
+        raise RuntimeError("reference binary failed: " + out.stdout[-400:] + out.stderr[-400:])
+    err = re.search(r"O error = (\S+)", out.stdout)
+    return float(m.group(1)), (float(err.group(1)) if err else None)
+
+
+def _port_sample_seconds(B):
+    import numpy as np
+    import oracle_lib as ol
+    S, Hq, Hkv = 4096, 128, 8
+    q = ol.randn_bf16((B, Hq, 128), 1)
+    k = ol.randn_bf16((B, S, Hkv, 128), 2)
+    v = ol.randn_bf16((B, S, Hkv, 128), 3)
+    t = time.perf_counter()
+    ol.decode(q, k, v, 1.0 / np.sqrt(128.0), 0, par_heads=False)
+    return time.perf_counter() - t
+
+
+def cpu_baseline_decode():
+    import oracle_lib as ol
+    cores = ol.lib().cllo_oracle_num_threads()
+    full = decode_bytes(60, 4096, 128, 8)
+    if os.path.exists(ol.REF_BIN):
+        secs, err = _run_ref_binary()
+        return {"value": full / secs / 1e12, "unit": "TB/s", "cores": cores, "kind": "reference", "seconds": secs,
+                "sample": "the whole headline workload (B=60, S=4096, Hq=128, Hkv=8), one run of upstream's "
+                          "unmodified test_decode_flash_gqa.cu CPU loop (OpenMP over batch); restatement vs "
+                          "upstream relative error printed by that program: %s" % err}
+    B = 16
+    secs = _port_sample_seconds(B)
+    return {"value": decode_bytes(B, 4096, 128, 8) / secs / 1e12, "unit": "TB/s", "cores": cores, "kind": "port",
+            "seconds": secs, "sample": "B=%d of the 60 sequences of the headline workload, C restatement" % B}
+
+
+def run_reference(args, rank, world):
+    """Upstream's CPU implementation on the host cores; rank 0 only."""
+    if rank != 0:
+        return
+    import oracle_lib as ol
+    ol.build_oracle()
+    cores = ol.lib().cllo_oracle_num_threads()
+    full = decode_bytes(60, 4096, 128, 8)
+    if os.path.exists(ol.REF_BIN):
+        n = max(1, min(args.steps, 4))  # each run regenerates 1 GB of inputs (~20-30 s); keep the arm to minutes
+        secs = [_run_ref_binary()[0] for _ in range(n)]
+        kind, sample = "reference", ("%d run(s) of upstream's unmodified test_decode_flash_gqa.cu CPU loop on the whole "
+                                     "headline workload; --steps %d requested, capped at 4" % (n, args.steps))
+        per = statistics.mean(secs)
+        units = full
+    else:
+        B = 16
+        n = max(1, min(args.steps, 10))
+        secs = [_port_sample_seconds(B) for _ in range(n)]
+        kind, sample = "port", "B=%d of 60 sequences per step, C restatement of upstream's loop, %d step(s)" % (B, n)
+        per = statistics.mean(secs)
+        units = decode_bytes(B, 4096, 128, 8)
+    value = units / per / 1e12
+    line = {"metric": "gqa_decode_achieved_hbm_tbps", "value": value, "unit": "TB/s", "n_gpus": world, "steps": n,
+            "warmup": 0, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "decode_b60: GQA decode B=60, S=4096, Hq=128, Hkv=8, D=128 on host cores"},
+            "cpu_baseline": {"value": value, "unit": "TB/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_b60",
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal"])
+    ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with: python -m torch.distributed.run --nnodes=1 "
+                             "--nproc-per-node %d --master-addr 127.0.0.1 bench.py --gpus %d ..." % (args.gpus, args.gpus))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,187 @@
+// C ABI of libcllo_flash_gqa.so (see include/cllo_flash_gqa.h).  Single translation unit: the kernels
+// share one device status word.
+#include "gqa_decode.cuh"
+#include "gqa_prefill.cuh"
+
+#include <cstdio>
+#include <cstring>
+
+using namespace cllo;
+
+extern "C" {
+
+int cllo_version(void) { return 100; }
+
+const char* cllo_status_string(int status) {
+    switch (status) {
+        case CLLO_OK: return "ok";
+        case CLLO_E_BAD_ARG: return "bad argument";
+        case CLLO_E_UNSUPPORTED: return "unsupported shape or device";
+        case CLLO_E_WORKSPACE: return "workspace missing or too small";
+        case CLLO_E_CUDA: return "CUDA call failed";
+        case CLLO_E_DEVICE_TIMEOUT: return "a bounded wait inside a kernel timed out";
+        default: return "unknown status";
+    }
+}
+
+int cllo_last_cuda_error(void) { return t_last_cuda_error; }
+
+int cllo_device_status(int detail[4]) {
+    int host[4] = {0, 0, 0, 0};
+    CLLO_CUDA_TRY(cudaDeviceSynchronize());
+    CLLO_CUDA_TRY(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+    if (host[0] != 0) {
+        const int zero[4] = {0, 0, 0, 0};
+        CLLO_CUDA_TRY(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+    }
+    if (detail) std::memcpy(detail, host, sizeof(host));
+    return host[0] == 0 ? CLLO_OK : CLLO_E_DEVICE_TIMEOUT;
+}
+
+int cllo_shutdown(void) {
+    int restore = 0;
+    if (cudaGetDevice(&restore) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return CLLO_OK;  // no device, nothing cached
+    }
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    for (int d = 0; d < kMaxDevices; ++d) {
+        if (g_dev[d].legacy_ws) {
+            if (cudaSetDevice(d) == cudaSuccess) (void)cudaFree(g_dev[d].legacy_ws);
+            g_dev[d].legacy_ws = nullptr;
+            g_dev[d].legacy_ws_bytes = 0;
+        }
+    }
+    (void)cudaSetDevice(restore);
+    (void)cudaGetLastError();
+    return CLLO_OK;
+}
+
+size_t cllo_gqa_decode_workspace_bytes(int B, int S, int Hq, int Hkv, int D, int num_workers) {
+    int sm = 0;
+    if (num_workers <= 0) {
+        DeviceInfo* di = nullptr;
+        if (current_device_info(&di) == CLLO_OK) sm = di->sm_count;
+        if (sm <= 0) sm = 256;  // no device visible: an upper bound for any current part
+    }
+    decode::Plan plan;
+    if (decode::make_plan(B, S, Hq, Hkv, D, num_workers, sm, &plan) != CLLO_OK) return 0;
+    return plan.ws_bytes;
+}
+
+int cllo_gqa_decode_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int sm_count, int out[6]) {
+    if (!out) return CLLO_E_BAD_ARG;
+    if (sm_count <= 0 && num_workers <= 0) {
+        DeviceInfo* di = nullptr;
+        int rc = current_device_info(&di);
+        if (rc != CLLO_OK) return rc;
+        sm_count = di->sm_count;
+    }
+    decode::Plan plan;
+    int rc = decode::make_plan(B, S, Hq, Hkv, D, num_workers, sm_count, &plan);
+    if (rc != CLLO_OK) return rc;
+    out[0] = plan.prm.W;
+    out[1] = plan.prm.n_t;
+    out[2] = static_cast<int>(plan.prm.T & 0xffffffffLL);
+    out[3] = static_cast<int>(plan.prm.T >> 32);
+    out[4] = plan.needs_merge ? 1 : 0;
+    out[5] = decode::kTok;
+    return CLLO_OK;
+}
+
+int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
+                         size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout,
+                         int num_workers, float* partial_out, void* stream) {
+    if (!q || !k || !v || (!o && !partial_out)) return CLLO_E_BAD_ARG;
+    if (kv_layout != CLLO_KV_BSHD && kv_layout != CLLO_KV_BHSD) return CLLO_E_BAD_ARG;
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || (o && !aligned_to(o, 16)) ||
+        (partial_out && !aligned_to(partial_out, 8)))
+        return CLLO_E_BAD_ARG;
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di);
+    if (rc != CLLO_OK) return rc;
+    if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
+    decode::Plan plan;
+    rc = decode::make_plan(B, S, Hq, Hkv, D, num_workers, di->sm_count, &plan);
+    if (rc != CLLO_OK) return rc;
+    if (!workspace || workspace_bytes < plan.ws_bytes || !aligned_to(workspace, 256)) return CLLO_E_WORKSPACE;
+
+    decode::Params& p = plan.prm;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.o = static_cast<__nv_bfloat16*>(o);
+    p.partial_out = partial_out;
+    p.ws = static_cast<float*>(workspace);
+    p.scale_log2 = scale * decode::kLog2e;
+    p.kv_layout = kv_layout;
+
+    CUtensorMap tm_k, tm_v;
+    rc = decode::encode_kv_map(&tm_k, k, B, S, Hkv, kv_layout);
+    if (rc != CLLO_OK) return rc;
+    rc = decode::encode_kv_map(&tm_v, v, B, S, Hkv, kv_layout);
+    if (rc != CLLO_OK) return rc;
+
+    if (!di->decode_attr_set) {
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
+        di->decode_attr_set = true;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    decode::decode_splitkv_kernel<<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(tm_k, tm_v, p);
+    CLLO_CUDA_TRY(cudaGetLastError());
+    if (plan.needs_merge) {
+        decode::decode_merge_kernel<<<static_cast<unsigned>(plan.units), decode::kD, 0, st>>>(p);
+        CLLO_CUDA_TRY(cudaGetLastError());
+    }
+    return CLLO_OK;
+}
+
+int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long rows, int D, void* stream) {
+    if (!partials || !o || nsplit <= 0 || rows <= 0) return CLLO_E_BAD_ARG;
+    if (D != decode::kD) return CLLO_E_UNSUPPORTED;
+    if (rows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+    decode::combine_rows_kernel<<<static_cast<unsigned>(rows), decode::kD, 0, static_cast<cudaStream_t>(stream)>>>(
+        partials, nsplit, rows, static_cast<__nv_bfloat16*>(o));
+    CLLO_CUDA_TRY(cudaGetLastError());
+    return CLLO_OK;
+}
+
+int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
+                              float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+    return prefill::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D,
+                           static_cast<cudaStream_t>(stream));
+}
+
+// Source-compatibility path for upstream's C++ launcher signature (no workspace argument): use the
+// caller's fp32 oIntermediate buffer [B,Hq,D] when it is large enough, else a per-device scratch that
+// this library allocates once and keeps (released by cllo_shutdown()).
+int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, float scale, void* o,
+                                float* o_intermediate, int B, int S, int Hq, int Hkv, int D) {
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di);
+    if (rc != CLLO_OK) return rc;
+    decode::Plan plan;
+    rc = decode::make_plan(B, S, Hq, Hkv, D, 0, di->sm_count, &plan);
+    if (rc != CLLO_OK) return rc;
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    const size_t inter_bytes = static_cast<size_t>(B) * Hq * D * sizeof(float);
+    if (o_intermediate && inter_bytes >= plan.ws_bytes && aligned_to(o_intermediate, 256)) {
+        ws = o_intermediate;
+        ws_bytes = inter_bytes;
+    } else {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (di->legacy_ws_bytes < plan.ws_bytes) {
+            if (di->legacy_ws) CLLO_CUDA_TRY(cudaFree(di->legacy_ws));
+            di->legacy_ws = nullptr;
+            di->legacy_ws_bytes = 0;
+            CLLO_CUDA_TRY(cudaMalloc(&di->legacy_ws, plan.ws_bytes));
+            di->legacy_ws_bytes = plan.ws_bytes;
+        }
+        ws = di->legacy_ws;
+        ws_bytes = di->legacy_ws_bytes;
+    }
+    return cllo_gqa_decode_bf16(q, k, v, scale, o, ws, ws_bytes, B, S, Hq, Hkv, D, CLLO_KV_BSHD, 0, nullptr,
+                                nullptr);
+}
+
+}  // extern "C"

@@ -1,0 +1,520 @@
+// Prefill (multi-token) GQA forward for sm_100a: tcgen05 tensor cores, accumulators in tensor memory,
+// TMA-fed double-buffered K/V pipeline.
+//
+// One thread block owns 256 query rows of one query head as two 128-row tiles ("ping" and "pong").
+// Per KV tile of 128 tokens it performs, for each of the two query tiles,
+//     S = Q K^T          tcgen05.mma  M=128 N=128 K=16 x8, Q and K from shared memory (K-major, 128B swizzle)
+//     P = online softmax 128 threads, one query row each, S read from tensor memory with tcgen05.ld
+//     O += P V           tcgen05.mma  M=128 N=128 K=16 x8, P from tensor memory (bf16, written with
+//                        tcgen05.st over the S columns), V from shared memory (MN-major, 128B swizzle)
+// so that the tensor pipe works on one tile while the other tile's softmax runs on the ALUs.
+//
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P aliases the first 64
+// columns of its S.  The running maximum is only raised (and O rescaled in tensor memory) when it
+// grew by more than 2^8, which keeps every probability below 256 and makes rescaling rare.
+//
+// Warp roles (320 threads): warps 0-3 softmax of tile 0, warps 4-7 softmax of tile 1 (a warp may only
+// touch the 32 tensor-memory lanes given by its index modulo 4), warp 8 TMA producer, warp 9 MMA issuer.
+// All hand-offs are mbarriers; every wait is bounded and records a status instead of hanging.
+#pragma once
+
+#include "common.cuh"
+#include "host_util.cuh"
+
+namespace cllo {
+namespace prefill {
+
+constexpr int kD = 128;
+constexpr int kBM = 128;          // query rows per tile
+constexpr int kBN = 128;          // kv tokens per tile
+constexpr int kTiles = 2;         // query tiles per block
+constexpr int kKvStages = 2;
+constexpr int kThreads = 320;
+constexpr int kHalfBytes = 128 * 128;        // [128 rows][64 dims] bf16 = 16 KB, one swizzled half tile
+constexpr int kTileBytes = 2 * kHalfBytes;   // 32 KB
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kTiles * kTileBytes;
+constexpr int kSmemV = kSmemK + kKvStages * kTileBytes;
+constexpr int kSmemBar = kSmemV + kKvStages * kTileBytes;
+constexpr int kNumBars = 1 + 4 * kKvStages + 3 * kTiles + 1;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+enum : int {
+    SITE_Q_FULL = SITE_PREFILL_BASE + 0,
+    SITE_K_FULL = SITE_PREFILL_BASE + 1,
+    SITE_V_FULL = SITE_PREFILL_BASE + 2,
+    SITE_K_EMPTY = SITE_PREFILL_BASE + 3,
+    SITE_V_EMPTY = SITE_PREFILL_BASE + 4,
+    SITE_S_FULL = SITE_PREFILL_BASE + 5,
+    SITE_P_FULL = SITE_PREFILL_BASE + 6,
+    SITE_O_FULL = SITE_PREFILL_BASE + 7,
+    SITE_DRAIN = SITE_PREFILL_BASE + 8,
+};
+
+struct Params {
+    __nv_bfloat16* o;
+    float* lse;  // nullable
+    float scale_log2;
+    int B, Sq, Skv, Hq, Hkv, G, causal, n_qp;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+// D(tmem) (+)= A(smem) * B(smem)
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D(tmem) (+)= A(tmem) * B(smem)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 columns + wait (see tmem_ld128_wait for why the wait is fused)
+__device__ __forceinline__ void tmem_ld32_wait(uint32_t taddr, float (&r)[32]) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+          "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+          "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr)
+        : "memory");
+}
+// 128 consecutive fp32 columns of this thread's lane.  The wait is part of the same statement so that no
+// use of the destination registers can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld128_wait(uint32_t taddr, float (&r)[128]) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x128.b32 {"
+        "%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
+        "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,"
+        "%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,"
+        "%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,"
+        "%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,"
+        "%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127"
+        "}, [%128];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+          "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+          "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31]),
+          "=r"(u[32]), "=r"(u[33]), "=r"(u[34]), "=r"(u[35]), "=r"(u[36]), "=r"(u[37]), "=r"(u[38]), "=r"(u[39]),
+          "=r"(u[40]), "=r"(u[41]), "=r"(u[42]), "=r"(u[43]), "=r"(u[44]), "=r"(u[45]), "=r"(u[46]), "=r"(u[47]),
+          "=r"(u[48]), "=r"(u[49]), "=r"(u[50]), "=r"(u[51]), "=r"(u[52]), "=r"(u[53]), "=r"(u[54]), "=r"(u[55]),
+          "=r"(u[56]), "=r"(u[57]), "=r"(u[58]), "=r"(u[59]), "=r"(u[60]), "=r"(u[61]), "=r"(u[62]), "=r"(u[63]),
+          "=r"(u[64]), "=r"(u[65]), "=r"(u[66]), "=r"(u[67]), "=r"(u[68]), "=r"(u[69]), "=r"(u[70]), "=r"(u[71]),
+          "=r"(u[72]), "=r"(u[73]), "=r"(u[74]), "=r"(u[75]), "=r"(u[76]), "=r"(u[77]), "=r"(u[78]), "=r"(u[79]),
+          "=r"(u[80]), "=r"(u[81]), "=r"(u[82]), "=r"(u[83]), "=r"(u[84]), "=r"(u[85]), "=r"(u[86]), "=r"(u[87]),
+          "=r"(u[88]), "=r"(u[89]), "=r"(u[90]), "=r"(u[91]), "=r"(u[92]), "=r"(u[93]), "=r"(u[94]), "=r"(u[95]),
+          "=r"(u[96]), "=r"(u[97]), "=r"(u[98]), "=r"(u[99]), "=r"(u[100]), "=r"(u[101]), "=r"(u[102]), "=r"(u[103]),
+          "=r"(u[104]), "=r"(u[105]), "=r"(u[106]), "=r"(u[107]), "=r"(u[108]), "=r"(u[109]), "=r"(u[110]), "=r"(u[111]),
+          "=r"(u[112]), "=r"(u[113]), "=r"(u[114]), "=r"(u[115]), "=r"(u[116]), "=r"(u[117]), "=r"(u[118]), "=r"(u[119]),
+          "=r"(u[120]), "=r"(u[121]), "=r"(u[122]), "=r"(u[123]), "=r"(u[124]), "=r"(u[125]), "=r"(u[126]), "=r"(u[127])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+        ::"r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+          "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+          "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
+          "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31]),
+          "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes.
+//   bits [0,14) start >> 4 | [16,30) leading-dim offset >> 4 | [32,46) stride-dim offset >> 4
+//   bits [46,48) = 1 (descriptor version of this architecture) | [61,64) = 2 (128-byte swizzle)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3fffu) | (static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16) |
+           (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: fp32 accumulate (bits 4-5 = 1), bf16 A and B (bits 7-9, 10-12 = 1),
+// B major-ness in bit 16 (0 = K-major, 1 = MN-major), N/8 in bits 17-22, M/16 in bits 24-28.
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar0 = base + kSmemBar;
+    // barrier map
+    const uint32_t bar_q_full = bar0;
+    auto bar_k_full = [&](int s) { return bar0 + 8 * (1 + s); };
+    auto bar_k_empty = [&](int s) { return bar0 + 8 * (1 + kKvStages + s); };
+    auto bar_v_full = [&](int s) { return bar0 + 8 * (1 + 2 * kKvStages + s); };
+    auto bar_v_empty = [&](int s) { return bar0 + 8 * (1 + 3 * kKvStages + s); };
+    auto bar_s_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + kTiles + t); };
+    auto bar_o_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 2 * kTiles + t); };
+    const uint32_t bar_drain = bar0 + 8 * (kNumBars - 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // block -> (batch, kv head, query tile pair, head in group); heads of one group are neighbours so
+    // that they stream the same K/V tiles through L2 together; heavy (late) causal pairs go first.
+    long long id = blockIdx.x;
+    const int g = static_cast<int>(id % p.G);
+    id /= p.G;
+    const int qp = p.n_qp - 1 - static_cast<int>(id % p.n_qp);
+    id /= p.n_qp;
+    const int kvh = static_cast<int>(id % p.Hkv);
+    const int b = static_cast<int>(id / p.Hkv);
+    const int h = kvh * p.G + g;
+    const int q0 = qp * (kTiles * kBM);
+
+    int n_kv = (p.Skv + kBN - 1) / kBN;
+    if (p.causal) {
+        const int last_row = q0 + kTiles * kBM - 1;
+        const int lim = last_row / kBN + 1;
+        n_kv = lim < n_kv ? lim : n_kv;
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q_full, 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(bar_k_full(s), 1);
+            mbar_init(bar_k_empty(s), 1);
+            mbar_init(bar_v_full(s), 1);
+            mbar_init(bar_v_empty(s), 1);
+        }
+        for (int t = 0; t < kTiles; ++t) {
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), kBM);
+            mbar_init(bar_o_full(t), 1);
+        }
+        mbar_init(bar_drain, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            mbar_arrive_expect_tx(bar_q_full, kTiles * kTileBytes);
+            for (int t = 0; t < kTiles; ++t) {
+                const uint32_t dst = base + kSmemQ + t * kTileBytes;
+                tma_load_4d(dst, &tm_q, bar_q_full, 0, q0 + t * kBM, h, b);
+                tma_load_4d(dst + kHalfBytes, &tm_q, bar_q_full, 64, q0 + t * kBM, h, b);
+            }
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % kKvStages;
+                const uint32_t use = static_cast<uint32_t>(j / kKvStages);
+                mbar_wait(bar_k_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_K_EMPTY, j);
+                mbar_arrive_expect_tx(bar_k_full(s), kTileBytes);
+                const uint32_t kd = base + kSmemK + s * kTileBytes;
+                tma_load_4d(kd, &tm_k, bar_k_full(s), 0, j * kBN, kvh, b);
+                tma_load_4d(kd + kHalfBytes, &tm_k, bar_k_full(s), 64, j * kBN, kvh, b);
+                mbar_wait(bar_v_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_V_EMPTY, j);
+                mbar_arrive_expect_tx(bar_v_full(s), kTileBytes);
+                const uint32_t vd = base + kSmemV + s * kTileBytes;
+                tma_load_4d(vd, &tm_v, bar_v_full(s), 0, j * kBN, kvh, b);
+                tma_load_4d(vd + kHalfBytes, &tm_v, bar_v_full(s), 64, j * kBN, kvh, b);
+            }
+            if (*abort_flag) {
+                // a wait gave up somewhere: let the copies already issued land before the block retires
+                for (int j = (n_kv > kKvStages ? n_kv - kKvStages : 0); j < n_kv; ++j) {
+                    const int s = j % kKvStages;
+                    const uint32_t use = static_cast<uint32_t>(j / kKvStages);
+                    const long long t0 = clock64();
+                    while (!(mbar_try_wait(bar_k_full(s), use & 1u) && mbar_try_wait(bar_v_full(s), use & 1u)) &&
+                           clock64() - t0 < kWaitLimitCycles / 64) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // -------------------------------- MMA issuer --------------------------------
+        if (lane == 0) {
+            auto issue_s = [&](int t, int stage) {
+                const uint32_t qa = base + kSmemQ + t * kTileBytes;
+                const uint32_t ka = base + kSmemK + stage * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(tmem_base + t * kBN, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
+                              kIdescQK, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int stage, bool first) {
+                const uint32_t va = base + kSmemV + stage * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    tc_mma_ts(tmem_base + 256 + t * kD, tmem_base + t * kBN + ks * 8,
+                              smem_desc(va + ks * 2048, kHalfBytes, 1024), kIdescPV, (first && ks == 0) ? 0u : 1u);
+                }
+            };
+            mbar_wait(bar_q_full, 0, abort_flag, SITE_Q_FULL, 0);
+            mbar_wait(bar_k_full(0), 0, abort_flag, SITE_K_FULL, 0);
+            tc_fence_after();
+            issue_s(0, 0);
+            tc_commit(bar_s_full(0));
+            issue_s(1, 0);
+            tc_commit(bar_s_full(1));
+            tc_commit(bar_k_empty(0));
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % kKvStages;
+                const uint32_t use = static_cast<uint32_t>(j / kKvStages);
+                const int s1 = (j + 1) % kKvStages;
+                const uint32_t use1 = static_cast<uint32_t>((j + 1) / kKvStages);
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    if (t == 0) mbar_wait(bar_v_full(s), use & 1u, abort_flag, SITE_V_FULL, j);
+                    mbar_wait(bar_p_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_P_FULL, j);
+                    tc_fence_after();
+                    issue_pv(t, s, j == 0);
+                    tc_commit(bar_o_full(t));
+                    if (t == kTiles - 1) tc_commit(bar_v_empty(s));
+                    if (j + 1 < n_kv) {
+                        if (t == 0) {
+                            mbar_wait(bar_k_full(s1), use1 & 1u, abort_flag, SITE_K_FULL, j + 1);
+                            tc_fence_after();
+                        }
+                        issue_s(t, s1);
+                        tc_commit(bar_s_full(t));
+                        if (t == kTiles - 1) tc_commit(bar_k_empty(s1));
+                    }
+                }
+            }
+            // everything issued must have retired before tensor memory is released
+            tc_commit(bar_drain);
+            mbar_wait(bar_drain, 0, abort_flag, SITE_DRAIN, 0);
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar_drain, 0) && clock64() - t0 < kWaitLimitCycles / 64) {
+                }
+            }
+        }
+    } else {
+        // ------------------------- softmax + epilogue (one row per thread) -------------------------
+        const int t = warp >> 2;
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const int qi = q0 + t * kBM + row_in_tile;  // global query row
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t s_addr = tmem_base + lane_base + t * kBN;
+        const uint32_t o_addr = tmem_base + lane_base + 256 + t * kD;
+        float m = -INFINITY, l = 0.f;
+
+#pragma unroll 1
+        for (int j = 0; j < n_kv; ++j) {
+            mbar_wait(bar_s_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_S_FULL, j);
+            tc_fence_after();
+            float x[128];
+            tmem_ld128_wait(s_addr, x);
+
+            // scale into log2 units, mask, row maximum
+            int limit = p.Skv - 1 - j * kBN;  // last valid column of this tile
+            if (p.causal) {
+                const int cl = qi - j * kBN;
+                limit = cl < limit ? cl : limit;
+            }
+            const bool need_mask = (j * kBN + kBN > p.Skv) || (p.causal && (j * kBN + kBN - 1 > q0 + t * kBM));
+            float mx = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 128; ++c) {
+                    const float val = (c <= limit) ? x[c] * p.scale_log2 : -INFINITY;
+                    x[c] = val;
+                    mx = fmaxf(mx, val);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 128; ++c) {
+                    x[c] *= p.scale_log2;
+                    mx = fmaxf(mx, x[c]);
+                }
+            }
+
+            // raise the running maximum only when it pays (always on the first tile)
+            float alpha = 1.f;
+            const bool grow = (j == 0) || (mx > m + kRescaleThreshold);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m, mx);
+                if (j > 0) {
+                    alpha = fast_exp2(m - m_new);
+                    mbar_wait(bar_o_full(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float ov[32];
+                        tmem_ld32_wait(o_addr + c * 32, ov);
+                        uint32_t ou[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ou[e] = __float_as_uint(ov[e] * alpha);
+                        tmem_st32(o_addr + c * 32, ou);
+                    }
+                }
+                m = m_new;
+            }
+
+            // probabilities (bf16) into tensor memory over the S columns; row sum from the fp32 values
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int col = c * 64 + e * 2;
+                    const float p0 = fast_exp2(x[col] - m);
+                    const float p1 = fast_exp2(x[col + 1] - m);
+                    sum += p0 + p1;
+                    pk[e] = pack_bf16x2(p0, p1);
+                }
+                tmem_st32(s_addr + c * 32, pk);
+            }
+            l = l * alpha + sum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p_full(t));
+        }
+
+        // epilogue: O / l -> bf16, lse = m + log(l)
+        mbar_wait(bar_o_full(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
+        tc_fence_after();
+        const float inv_l = 1.f / l;
+        const bool row_ok = qi < p.Sq;
+        __nv_bfloat16* orow = p.o + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + qi) * kD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float ov[32];
+            tmem_ld32_wait(o_addr + c * 32, ov);
+            if (row_ok) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                    uint4 pkt;
+                    pkt.x = pack_bf16x2(ov[e + 0] * inv_l, ov[e + 1] * inv_l);
+                    pkt.y = pack_bf16x2(ov[e + 2] * inv_l, ov[e + 3] * inv_l);
+                    pkt.z = pack_bf16x2(ov[e + 4] * inv_l, ov[e + 5] * inv_l);
+                    pkt.w = pack_bf16x2(ov[e + 6] * inv_l, ov[e + 7] * inv_l);
+                    *reinterpret_cast<uint4*>(orow + c * 32 + e) = pkt;
+                }
+            }
+        }
+        if (row_ok && p.lse)
+            p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] = (m + log2f(l)) * kLn2;
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, int S) {
+    const uint64_t row = static_cast<uint64_t>(kD) * 2;
+    const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(S), static_cast<uint64_t>(H),
+                              static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {row, row * S, row * S * H};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    return encode_bf16_4d(map, basep, dims, strides, box);
+}
+
+static int launch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
+                  int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+    if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return CLLO_E_BAD_ARG;
+    if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16)) return CLLO_E_BAD_ARG;
+    if (D != kD) return CLLO_E_UNSUPPORTED;
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di);
+    if (rc != CLLO_OK) return rc;
+    if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
+
+    Params p;
+    p.o = static_cast<__nv_bfloat16*>(o);
+    p.lse = lse;
+    p.scale_log2 = scale * kLog2e;
+    p.B = B;
+    p.Sq = Sq;
+    p.Skv = Skv;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = Hq / Hkv;
+    p.causal = causal ? 1 : 0;
+    p.n_qp = (Sq + kTiles * kBM - 1) / (kTiles * kBM);
+    const long long blocks = static_cast<long long>(B) * Hq * p.n_qp;
+    if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+
+    CUtensorMap tm_q, tm_k, tm_v;
+    if ((rc = encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
+    if ((rc = encode_bhsd_map(&tm_k, k, B, Hkv, Skv)) != CLLO_OK) return rc;
+    if ((rc = encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
+
+    if (!di->prefill_attr_set) {
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kSmemBytes));
+        di->prefill_attr_set = true;
+    }
+    prefill_fwd_kernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+    CLLO_CUDA_TRY(cudaGetLastError());
+    return CLLO_OK;
+}
+
+}  // namespace prefill
+}  // namespace cllo

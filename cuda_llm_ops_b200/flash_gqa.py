@@ -1,0 +1,253 @@
+"""Host-side mirror of upstream's GQA operator interface, on top of the C ABI.
+
+Upstream (LiuYiyang-Canton/cuda_llm_ops) exposes this path three ways; each has a same-named function here
+with the same argument meaning and error behaviour:
+
+* ``LaunchFlashGqaBf16Kernel``                 C++ launcher, include/cplusplus/FlashGQA/decode_flash_gqa_kernel.cuh:28-38
+  (Q [B,Hq,D], K/V [B,S,Hkv,D], O [B,Hq,D]; silently does nothing on shapes it cannot handle,
+  src/cplusplus/FlashGQA/decode_flash_gqa_kernel.cu:416-437)
+* ``launch_decode_flash_gqa_bf16_kernel``      Triton launcher, src/python/Triton/decode_flash_gqa_kernel.py:137-196
+  (Q [B,Hq,Sq,D], K/V [B,Hkv,S,D]; raises ValueError on bad inputs; only query row 0 is used)
+* ``launch_flash_gqa_forward_bf16_kernel``     Triton launcher, src/python/Triton/flash_gqa_kernel.py:185-338
+  (3-D or 4-D tensors, causal=True default, returns (out, lse))
+
+torch is used for device memory and streams only.  Nothing here computes attention on the host and there
+is no fallback: without the compiled library or on a non-CUDA tensor these functions raise.
+"""
+import math
+
+import torch
+
+from . import _lib
+
+KV_BSHD = _lib.KV_BSHD
+KV_BHSD = _lib.KV_BHSD
+HEAD_DIM = 128
+PARTIAL_WIDTH = HEAD_DIM + 2
+
+_workspaces = {}
+
+
+def _stream_ptr():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def decode_workspace_bytes(B, S, Hq, Hkv, D=HEAD_DIM, num_workers=0):
+    return int(_lib.load().cllo_gqa_decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers))
+
+
+def _workspace(device, nbytes):
+    """A per-device scratch tensor, grown on demand (torch owns the memory)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _require_cuda_bf16(name, t):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor: this library has no CPU path" % name)
+    if t.dtype != torch.bfloat16:
+        raise ValueError("%s must be bf16" % name)
+
+
+def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=None, num_workers=0, workspace=None):
+    """Split-KV decode through ``cllo_gqa_decode_bf16``.
+
+    q [B,Hq,D]; k, v [B,S,Hkv,D] (KV_BSHD) or [B,Hkv,S,D] (KV_BHSD); returns out [B,Hq,D] bf16, or, when
+    ``partial_out`` ([B,Hq,D+2] fp32) is given, fills and returns that packed (O, m, l) tensor instead.
+    """
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t)
+    if q.dim() != 3 or k.dim() != 4 or v.shape != k.shape:
+        raise ValueError("expected q [B,Hq,D] and k, v of identical 4-D shape")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("q, k and v must be contiguous")
+    B, Hq, D = q.shape
+    if kv_layout == KV_BSHD:
+        Bk, S, Hkv, Dk = k.shape
+    elif kv_layout == KV_BHSD:
+        Bk, Hkv, S, Dk = k.shape
+    else:
+        raise ValueError("unknown kv_layout")
+    if Bk != B or Dk != D:
+        raise ValueError("q, k and v must share batch and head_dim")
+    if Hq % Hkv != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        nbytes = decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers)
+        if workspace is None:
+            workspace = _workspace(q.device, nbytes)
+        if partial_out is not None:
+            if partial_out.dtype != torch.float32 or tuple(partial_out.shape) != (B, Hq, D + 2) \
+                    or not partial_out.is_contiguous() or not partial_out.is_cuda:
+                raise ValueError("partial_out must be a contiguous CUDA fp32 tensor of shape [B,Hq,D+2]")
+            o_ptr, p_ptr, result = None, partial_out.data_ptr(), partial_out
+        else:
+            if out is None:
+                out = torch.empty_like(q)
+            if out.dtype != torch.bfloat16 or out.shape != q.shape or not out.is_contiguous():
+                raise ValueError("Output tensor must be contiguous bf16 of q's shape")
+            o_ptr, p_ptr, result = out.data_ptr(), None, out
+        rc = lib.cllo_gqa_decode_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), float(scale), o_ptr,
+                                      workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                      B, S, Hq, Hkv, D, kv_layout, num_workers, p_ptr, _stream_ptr())
+    _lib.check(rc, "cllo_gqa_decode_bf16")
+    return result
+
+
+def gqa_combine(partials, out=None):
+    """LSE merge through ``cllo_gqa_combine_bf16``: partials [nsplit,B,Hq,D+2] fp32 -> out [B,Hq,D] bf16."""
+    if not partials.is_cuda or partials.dtype != torch.float32 or partials.dim() != 4 \
+            or partials.shape[-1] != PARTIAL_WIDTH or not partials.is_contiguous():
+        raise ValueError("partials must be a contiguous CUDA fp32 tensor [nsplit,B,Hq,%d]" % PARTIAL_WIDTH)
+    nsplit, B, Hq, _ = partials.shape
+    if out is None:
+        out = torch.empty((B, Hq, HEAD_DIM), dtype=torch.bfloat16, device=partials.device)
+    with torch.cuda.device(partials.device):
+        rc = _lib.load().cllo_gqa_combine_bf16(partials.data_ptr(), nsplit, out.data_ptr(), B * Hq, HEAD_DIM,
+                                               _stream_ptr())
+    _lib.check(rc, "cllo_gqa_combine_bf16")
+    return out
+
+
+def LaunchFlashGqaBf16Kernel(q, k, v, scale, o, oIntermediate, batchSize, seqLength, numQueryHeads, numKvHeads,
+                             headDim):
+    """Mirror of upstream's C++ launcher (decode_flash_gqa_kernel.cuh:28-38), tensors instead of pointers.
+
+    Like upstream it returns None and does nothing on shapes it rejects
+    (decode_flash_gqa_kernel.cu:416-437) -- but it rejects far fewer: any group size and any S >= 1 work;
+    only headDim != 128 or non-divisible head counts are refused.  ``oIntermediate`` ([B,Hq,D] fp32) is used
+    as scratch when it is big enough, exactly as upstream uses it.
+    """
+    if batchSize <= 0 or seqLength <= 0 or numQueryHeads <= 0 or numKvHeads <= 0 or headDim <= 0:
+        return
+    if numQueryHeads % numKvHeads != 0 or headDim != HEAD_DIM:
+        return
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
+        _require_cuda_bf16(name, t)
+    with torch.cuda.device(q.device):
+        ws = None
+        need = decode_workspace_bytes(batchSize, seqLength, numQueryHeads, numKvHeads, headDim)
+        if oIntermediate is not None and oIntermediate.is_cuda and \
+                oIntermediate.numel() * oIntermediate.element_size() >= need and oIntermediate.data_ptr() % 256 == 0:
+            ws = oIntermediate.view(torch.uint8).view(-1) if oIntermediate.is_contiguous() else None
+        if ws is None:
+            ws = _workspace(q.device, need)
+        rc = _lib.load().cllo_gqa_decode_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), float(scale), o.data_ptr(),
+                                              ws.data_ptr(), ws.numel(), batchSize, seqLength, numQueryHeads,
+                                              numKvHeads, headDim, KV_BSHD, 0, None, _stream_ptr())
+    _lib.check(rc, "cllo_gqa_decode_bf16")
+
+
+def launch_decode_flash_gqa_bf16_kernel(q, k, v, out=None):
+    """Mirror of upstream's Triton decode launcher (decode_flash_gqa_kernel.py:137-196).
+
+    q [B,Hq,Sq,D], k, v [B,Hkv,S,D] -> out [B,Hq,Sq,D]; scale is fixed at 1/sqrt(D) (:180).  As upstream,
+    only query row 0 of each head is read and written (:76,111).
+    """
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("Flash GQA decoding expects bf16 inputs")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("Flash GQA decoding kernel expects contiguous Q/K/V tensors")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("Q, K, and V must be 4-D")
+    batch, q_heads, seqlen_q, head_dim = q.shape
+    k_batch, num_kv_heads, seqlen_kv, k_head_dim = k.shape
+    v_batch, v_heads, v_seqlen, v_head_dim = v.shape
+    if batch != k_batch or batch != v_batch:
+        raise ValueError("Q, K, and V must share batch dimension")
+    if seqlen_kv != v_seqlen:
+        raise ValueError("K and V must share sequence length")
+    if k_head_dim != v_head_dim or head_dim != k_head_dim:
+        raise ValueError("Q, K, and V must share head_dim")
+    if v_heads != num_kv_heads:
+        raise ValueError("K and V must share number of KV heads")
+    if q_heads % num_kv_heads != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    if head_dim != HEAD_DIM:
+        raise ValueError("this build supports head_dim == 128 only")
+    if out is None:
+        out = torch.empty_like(q)
+    if not out.is_contiguous():
+        raise ValueError("Output tensor must be contiguous")
+    if seqlen_q == 1:
+        gqa_decode(q.view(batch, q_heads, head_dim), k, v, kv_layout=KV_BHSD, out=out.view(batch, q_heads, head_dim))
+    else:
+        row0 = gqa_decode(q[:, :, 0, :].contiguous(), k, v, kv_layout=KV_BHSD)
+        out[:, :, 0, :] = row0
+    return out
+
+
+def launch_flash_gqa_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None, causal=True, **_tuning):
+    """Mirror of upstream's Triton prefill launcher (flash_gqa_kernel.py:185-338).
+
+    Accepts [Hq,Sq,D] / [Hkv,Skv,D] or the batched 4-D forms, ``causal=True`` by default (:192), returns
+    ``(out, lse)`` with lse = rowmax + log(rowsum) in fp32 (:132).  Upstream's Triton tuning keywords
+    (block_kv_sub, num_warps, num_stages) are accepted and ignored.
+    """
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("Flash GQA forward expects bf16 inputs")
+    if q.dim() not in (3, 4):
+        raise ValueError("Q must be 3D or 4D")
+    if k.dim() != q.dim() or v.dim() != q.dim():
+        raise ValueError("Q, K, and V must have matching ranks")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t)
+    squeeze = q.dim() == 3
+    qb, kb, vb = (t.contiguous().unsqueeze(0) if squeeze else t.contiguous() for t in (q, k, v))
+    batch, q_heads, seqlen_q, head_dim_qk = qb.shape
+    _, num_kv_heads, seqlen_kv, k_head_dim = kb.shape
+    _, v_heads, v_seqlen, head_dim_v = vb.shape
+    if seqlen_kv != v_seqlen:
+        raise ValueError("K and V must share sequence length")
+    if k_head_dim != head_dim_qk:
+        raise ValueError("Q and K must share head_dim_qk")
+    if v_heads != num_kv_heads:
+        raise ValueError("K and V must share number of KV heads")
+    if q_heads % num_kv_heads != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    if head_dim_qk != HEAD_DIM or head_dim_v != HEAD_DIM:
+        raise ValueError("this build supports head_dim == 128 only")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim_qk)
+    if out is None:
+        out_b = torch.empty((batch, q_heads, seqlen_q, head_dim_v), device=qb.device, dtype=qb.dtype)
+    else:
+        if out.dim() != q.dim():
+            raise ValueError("Output must be 3D when Q is 3D" if squeeze else "Output must be 4D when Q is 4D")
+        if not out.is_contiguous():
+            raise ValueError("Output tensor must be contiguous")
+        out_b = out.unsqueeze(0) if squeeze else out
+    if tuple(out_b.shape) != (batch, q_heads, seqlen_q, head_dim_v):
+        raise ValueError("Output must have shape [batch, q_heads, seqlen_q, head_dim_v]")
+    if lse is None:
+        lse_b = torch.empty((batch, q_heads, seqlen_q), device=qb.device, dtype=torch.float32)
+    else:
+        if lse.dim() != q.dim() - 1:
+            raise ValueError("LSE must be 2D when Q is 3D" if squeeze else "LSE must be 3D when Q is 4D")
+        if not lse.is_contiguous() or lse.dtype != torch.float32:
+            raise ValueError("LSE must be contiguous fp32")
+        lse_b = lse.unsqueeze(0) if squeeze else lse
+    with torch.cuda.device(qb.device):
+        rc = _lib.load().cllo_gqa_prefill_fwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), float(scale),
+                                                   1 if causal else 0, out_b.data_ptr(), lse_b.data_ptr(),
+                                                   batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
+                                                   _stream_ptr())
+    _lib.check(rc, "cllo_gqa_prefill_fwd_bf16")
+    if squeeze:
+        return out_b.squeeze(0), lse_b.squeeze(0)
+    return out_b, lse_b
+
+
+def device_status():
+    """Synchronise and return (status, detail) from ``cllo_device_status``."""
+    import ctypes
+    detail = (ctypes.c_int * 4)()
+    rc = _lib.load().cllo_device_status(detail)
+    return rc, list(detail)

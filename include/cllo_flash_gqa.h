@@ -1,0 +1,110 @@
+/*
+ * C ABI of the B200 (sm_100a) flash grouped-query attention library  --  libcllo_flash_gqa.so
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless the name says host.
+ * All functions are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream), act on the CURRENT device, return 0 on success or a negative CLLO_E_* code,
+ * and never abort the process or trap on the device.  The library allocates no device memory
+ * except where a function's comment says so.
+ *
+ * Tensors are bf16 (uint16 bit patterns), accumulation is fp32.  head_dim must be 128.
+ *
+ * Each entry point names the upstream (LiuYiyang-Canton/cuda_llm_ops) interface it stands in for.
+ */
+#ifndef CLLO_FLASH_GQA_H_
+#define CLLO_FLASH_GQA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CLLO_OK 0
+#define CLLO_E_BAD_ARG (-1)       /* null / misaligned pointer, non-positive size, Hq % Hkv != 0 */
+#define CLLO_E_UNSUPPORTED (-2)   /* head_dim != 128, wrong GPU architecture */
+#define CLLO_E_WORKSPACE (-3)     /* workspace missing or too small */
+#define CLLO_E_CUDA (-4)          /* a CUDA call failed; see cllo_last_cuda_error() */
+#define CLLO_E_DEVICE_TIMEOUT (-6) /* a bounded wait inside a kernel gave up; results are invalid */
+
+/* K/V cache layouts */
+#define CLLO_KV_BSHD 0 /* [B, S, Hkv, D]  upstream C++ layout (decode_flash_gqa_kernel.cu:144-148) */
+#define CLLO_KV_BHSD 1 /* [B, Hkv, S, D]  upstream Triton layout (decode_flash_gqa_kernel.py:50-53) */
+
+/* Width of one packed partial row: D un-normalised fp32 outputs, then m, then l. */
+#define CLLO_PARTIAL_WIDTH(D) ((D) + 2)
+
+int cllo_version(void);
+const char* cllo_status_string(int status);
+/* cudaError_t value of the most recent failing CUDA call made by this library on this thread. */
+int cllo_last_cuda_error(void);
+/* Synchronises the current device, returns CLLO_OK or CLLO_E_DEVICE_TIMEOUT if any kernel of this
+ * library recorded a timed-out wait since the last call, and clears the record.  detail (host,
+ * nullable) receives {code, block, site, aux}. */
+int cllo_device_status(int detail[4]);
+/* Frees the per-device scratch that LaunchFlashGqaBf16Kernel's compatibility path may have cached. */
+int cllo_shutdown(void);
+
+/*
+ * Single-token GQA decode:  O[b, h, :] = softmax(scale * q[b,h,:] . K[b,:,h/G,:]^T) V[b,:,h/G,:]
+ *
+ * Stands in for decode_flash_gqa_bf16_kernel + LaunchFlashGqaBf16Kernel
+ * (src/cplusplus/FlashGQA/decode_flash_gqa_kernel.cu:119-389, :405-470; declared in
+ * include/cplusplus/FlashGQA/decode_flash_gqa_kernel.cuh:28-38) and for the Triton twin
+ * launch_decode_flash_gqa_bf16_kernel (src/python/Triton/decode_flash_gqa_kernel.py:137-196).
+ * Unlike upstream it accepts any group size G = Hq/Hkv >= 1 and any S >= 1.
+ *
+ *   q [B,Hq,D]   k,v per kv_layout   o [B,Hq,D] bf16
+ *   workspace / workspace_bytes: scratch of at least cllo_gqa_decode_workspace_bytes(...) bytes,
+ *       256-byte aligned.  The KV range of every (batch, kv head) is cut into equal shares for
+ *       `num_workers` persistent thread blocks; shares that cover only part of a head leave fp32
+ *       partials (O, m, l) in the workspace and a second kernel merges them by log-sum-exp.
+ *   num_workers: 0 = one per SM of the current device.
+ *   partial_out (nullable): when given, `o` is ignored and the call writes, for every (b, h), one
+ *       packed fp32 row [D+2] = {un-normalised O, m = max scaled score, l = sum exp(score - m)} of
+ *       THIS call's KV range.  This is what a KV-position-sharded caller all-gathers and feeds to
+ *       cllo_gqa_combine_bf16.
+ */
+size_t cllo_gqa_decode_workspace_bytes(int B, int S, int Hq, int Hkv, int D, int num_workers);
+int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scale, void* o,
+                         void* workspace, size_t workspace_bytes,
+                         int B, int S, int Hq, int Hkv, int D,
+                         int kv_layout, int num_workers, float* partial_out, void* stream);
+
+/* How a decode call would be cut up: plan[0] = workers actually launched, plan[1] = KV tiles per
+ * (batch, kv head, 16-query-head block), plan[2..3] = total tiles (low, high 32 bits), plan[4] = 1 if the
+ * merge pass runs, plan[5] = tokens per tile.  Host-only arithmetic; sm_count <= 0 means "ask the device". */
+int cllo_gqa_decode_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int sm_count, int plan[6]);
+
+/* Upstream's launcher signature without a workspace argument (LaunchFlashGqaBf16Kernel,
+ * decode_flash_gqa_kernel.cuh:28-38): K/V in CLLO_KV_BSHD, default stream.  Uses o_intermediate
+ * ([B,Hq,D] fp32, upstream's scratch argument) as workspace when it is large enough; otherwise it
+ * cudaMallocs one scratch buffer per device on first use and keeps it until cllo_shutdown(). */
+int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, float scale, void* o,
+                                float* o_intermediate, int B, int S, int Hq, int Hkv, int D);
+
+/*
+ * Log-sum-exp merge of nsplit packed partials:  partials [nsplit][rows][D+2] fp32 -> o [rows][D] bf16.
+ * rows = B*Hq.  Splits with l == 0 are ignored.  Same (m, l) monoid as the running update in
+ * decode_flash_gqa_kernel.cu:353-371 and TileMaxSumReduce (src/cplusplus/Softmax/softmax_kernel.cu:21-34).
+ * Upstream has no multi-GPU path; this is the second pass of the split-KV decode exposed for callers
+ * that shard one sequence's KV cache by position across GPUs.
+ */
+int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long rows, int D, void* stream);
+
+/*
+ * Multi-token (prefill) GQA forward:  O = softmax(mask(scale * Q K^T)) V,  lse = m + log(l).
+ * Stands in for flash_gqa_forward_bf16_kernel + launch_flash_gqa_forward_bf16_kernel
+ * (src/python/Triton/flash_gqa_kernel.py:16-138, :185-338).  Layout as upstream:
+ *   q,o [B,Hq,Sq,D]   k,v [B,Hkv,Skv,D]   lse [B,Hq,Sq] fp32 (nullable)
+ * causal != 0 keeps kv <= q (top-left aligned, flash_gqa_kernel.py:104,114).
+ */
+int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal,
+                              void* o, float* lse,
+                              int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLLO_FLASH_GQA_H_ */

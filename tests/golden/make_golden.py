@@ -1,0 +1,79 @@
+"""Generate the golden vectors in this directory from the UPSTREAM torch oracles.
+
+Run once, in a container that has the upstream checkout (it is not needed to run the tests):
+
+    python tests/golden/make_golden.py --reference /root/reference
+
+It imports, unmodified,
+  * ``flash_gqa_reference``          examples/python/Triton/test_decode_flash_gqa_kernel.py:26-79
+    (tiled, non-causal, any number of query rows), and
+  * ``flash_gqa_forward_reference``  examples/python/Triton/test_flash_gqa_kernel.py:27-94
+    (full softmax, causal, returns the log-sum-exp),
+feeds them small seeded N(0,1) bf16 tensors and stores inputs and outputs (bf16 as uint16 bit
+patterns) in ``gqa_golden.npz``.  The tests compare both the C oracle and the CUDA kernels with
+these files, so the oracle is pinned to upstream's own code rather than to itself.
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(args.reference, "examples", "python", "Triton"))
+    from test_decode_flash_gqa_kernel import flash_gqa_reference  # noqa: E402
+    from test_flash_gqa_kernel import flash_gqa_forward_reference  # noqa: E402
+
+    out = {}
+    meta = []
+
+    # --- decode (one query row) and non-causal multi-row cases: layout [B,H,S,D] -------------
+    decode_cases = [
+        # name,            B, Hq, Hkv, Sq, Skv, std
+        ("decode_g4",      2, 8, 2, 1, 192, 1.0),
+        ("decode_g16_rag", 1, 16, 1, 1, 200, 1.0),   # ragged last tile (200 = 128 + 72)
+        ("decode_g8_tiny", 1, 8, 1, 1, 77, 1.0),     # shorter than one tile
+        ("decode_g1",      1, 2, 2, 1, 130, 0.5),
+        ("noncausal_g2",   1, 4, 2, 48, 160, 1.0),   # pins the non-causal prefill path
+    ]
+    for i, (name, B, Hq, Hkv, Sq, Skv, std) in enumerate(decode_cases):
+        g = torch.Generator().manual_seed(1000 + i)
+        q = (torch.randn(B, Hq, Sq, 128, generator=g) * std).to(torch.bfloat16)
+        k = (torch.randn(B, Hkv, Skv, 128, generator=g) * std).to(torch.bfloat16)
+        v = (torch.randn(B, Hkv, Skv, 128, generator=g) * std).to(torch.bfloat16)
+        o = flash_gqa_reference(q, k, v)
+        out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
+        meta.append(name)
+
+    # --- causal prefill with log-sum-exp: upstream takes un-batched [H,S,D] -------------------
+    prefill_cases = [
+        ("causal_g4", 4, 1, 160),
+        ("causal_g1", 2, 2, 96),
+    ]
+    for i, (name, Hq, Hkv, S) in enumerate(prefill_cases):
+        g = torch.Generator().manual_seed(2000 + i)
+        q = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        o, lse = flash_gqa_forward_reference(q, k, v, return_lse=True)
+        out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
+        meta.append(name)
+
+    out["cases"] = np.array(meta)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gqa_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes;", "torch", torch.__version__)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,95 @@
+"""Parity of the tcgen05 prefill kernel (through the C ABI) with the CPU oracle and upstream's golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as ol
+from gpu_util import assert_clean_status, to_bits, to_dev
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / np.sqrt(128.0)
+LSE_TOL = 2e-3  # fp32 log-sum-exp, absolute
+
+
+def _run(q, k, v, causal, scale=None):
+    import cuda_llm_ops_b200 as ops
+    out, lse = ops.launch_flash_gqa_forward_bf16_kernel(to_dev(q), to_dev(k), to_dev(v), scale=scale, causal=causal)
+    torch.cuda.synchronize()
+    return to_bits(out), lse.cpu().numpy()
+
+
+@pytest.mark.parametrize("name,causal", [("causal_g4", True), ("causal_g1", True)])
+def test_golden_causal_vectors_from_upstream_torch_oracle(golden, name, causal):
+    # upstream's un-batched 3-D calling convention
+    got_o, got_lse = _run(golden[name + "/q"], golden[name + "/k"], golden[name + "/v"], causal)
+    ol.assert_parity(got_o, golden[name + "/o"], name)
+    assert np.allclose(got_lse, golden[name + "/lse"], atol=LSE_TOL)
+    assert_clean_status()
+
+
+def test_golden_noncausal_vectors_from_upstream_torch_oracle(golden):
+    name = "noncausal_g2"
+    got_o, _ = _run(golden[name + "/q"], golden[name + "/k"], golden[name + "/v"], False)
+    ol.assert_parity(got_o, golden[name + "/o"], name)
+
+
+# (B, Hq, Hkv, Sq, Skv)
+CASES = [
+    (1, 4, 1, 256, 256),
+    (1, 2, 2, 128, 128),
+    (2, 8, 2, 384, 384),      # odd number of 128-row tiles
+    (1, 4, 2, 200, 200),      # ragged query and kv tails
+    (1, 2, 1, 1, 1),
+    (1, 3, 1, 70, 300),       # Sq != Skv
+    (1, 16, 1, 640, 640),     # group 16, like the headline prefill config
+    (1, 2, 1, 1024, 1024),
+]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv", CASES)
+def test_parity_with_cpu_oracle(B, Hq, Hkv, Sq, Skv, causal):
+    q = ol.randn_bf16((B, Hq, Sq, 128), 101)
+    k = ol.randn_bf16((B, Hkv, Skv, 128), 102)
+    v = ol.randn_bf16((B, Hkv, Skv, 128), 103)
+    want_o, want_lse = ol.prefill(q, k, v, SCALE, causal)
+    got_o, got_lse = _run(q, k, v, causal)
+    ol.assert_parity(got_o, want_o, "B%d Hq%d Hkv%d Sq%d Skv%d causal%d" % (B, Hq, Hkv, Sq, Skv, causal))
+    assert np.allclose(got_lse, want_lse, atol=LSE_TOL), np.abs(got_lse - want_lse).max()
+    assert_clean_status()
+
+
+def test_peaked_scores_exercise_the_rescale_path():
+    # growing keys make the running maximum jump by more than the lazy-rescale threshold many times
+    B, Hq, Hkv, S = 1, 2, 1, 1024
+    q = ol.randn_bf16((B, Hq, S, 128), 111, std=2.0)
+    kf = np.random.default_rng(112).standard_normal((B, Hkv, S, 128)).astype(np.float32)
+    kf *= np.linspace(0.2, 4.0, S, dtype=np.float32)[None, None, :, None]
+    k = ol.f32_to_bf16_bits(kf)
+    v = ol.randn_bf16((B, Hkv, S, 128), 113)
+    for causal in (False, True):
+        want_o, want_lse = ol.prefill(q, k, v, SCALE, causal)
+        got_o, got_lse = _run(q, k, v, causal)
+        ol.assert_parity(got_o, want_o, "peaked causal=%d" % causal)
+        assert np.allclose(got_lse, want_lse, atol=5e-3, rtol=1e-4)
+    assert_clean_status()
+
+
+def test_headline_prefill_shape_sampled_rows():
+    """Baseline config 3 (B=1, S=4096, Hq=16, Hkv=1, non-causal) at full size; rows sampled for the oracle."""
+    import cuda_llm_ops_b200 as ops
+    Hq, S = 16, 4096
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    q = torch.randn((1, Hq, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn((1, 1, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn((1, 1, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+    for causal in (False, True):
+        out, lse = ops.launch_flash_gqa_forward_bf16_kernel(q, k, v, causal=causal)
+        torch.cuda.synchronize()
+        got = to_bits(out)
+        qb, kb, vb = to_bits(q), to_bits(k), to_bits(v)
+        for r0 in (0, 127, 1920, 4064):
+            want_o, want_lse = ol.prefill(qb, kb, vb, SCALE, causal, row_begin=r0, row_end=r0 + 32)
+            ol.assert_parity(got[:, :, r0:r0 + 32], want_o[:, :, r0:r0 + 32], "rows %d causal=%d" % (r0, causal))
+            assert np.allclose(lse.cpu().numpy()[:, :, r0:r0 + 32], want_lse[:, :, r0:r0 + 32], atol=LSE_TOL)
+    assert_clean_status()
