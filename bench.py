@@ -137,7 +137,7 @@ def run_ours(args, rank, world, local_rank):
 
     extra = {}
     if wl == "decode_b60":
-        B, S, Hq, Hkv = 60, 4096, 128, 8
+        B, S, Hq, Hkv = (args.batch or 60), 4096, 128, 8
         layout = ops.KV_BSHD if args.layout == "bshd" else ops.KV_BHSD
         kshape = (B, S, Hkv, 128) if layout == ops.KV_BSHD else (B, Hkv, S, 128)
         q, k, v = randn_bf16((B, Hq, 128)), randn_bf16(kshape), randn_bf16(kshape)
@@ -148,10 +148,10 @@ def run_ours(args, rank, world, local_rank):
         metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
         launches_per_step = 2
         scaling = "weak"
-        config = {"workload": "decode_b60: GQA decode B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, one query token, "
-                              "K/V %s, N(0,1) seeded" % ("[B,S,Hkv,D]" if layout == ops.KV_BSHD else "[B,Hkv,S,D]"),
+        config = {"workload": "decode_b60: GQA decode B=%d per GPU, S=4096, Hq=128, Hkv=8, D=128, one query token, "
+                              "K/V %s, N(0,1) seeded" % (B, "[B,S,Hkv,D]" if layout == ops.KV_BSHD else "[B,Hkv,S,D]"),
                   "global_batch": B * world, "kv_seq_len": S, "sharding": "batch (no collective)",
-                  "l2": "inputs (1.0 GB per GPU) exceed the 126 MB L2; no flush needed"}
+                  "l2": "inputs (%.2f GB per GPU) exceed the 126 MB L2; no flush needed" % (units_per_rank / 1e9)}
         host_in = [q, k, v]
     elif wl == "decode_long":
         S_total, Hq, Hkv = 1 << 20, 64, 8
@@ -249,7 +249,7 @@ def run_ours(args, rank, world, local_rank):
     else:
         total_ms = t0.elapsed_time(t1)
     # keep the GPU busy with the same kernel a little longer so that the clock samples see load
-    if rank == 0 and (t_end - t_begin) < 0.6:
+    if rank == 0 and (t_end - t_begin) < 0.6 and not args.profile:
         reps = int(min(20000, 0.6 / max(total_ms / args.steps / 1e3, 1e-6)))
         for _ in range(reps):
             step_fn()
@@ -267,7 +267,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end: pinned host buffers -> device -> kernel -> host ----
     e2e = None
-    if wl in ("decode_b60", "prefill_nc"):
+    if wl in ("decode_b60", "prefill_nc") and not args.profile:
         host = [t.cpu().pin_memory() for t in host_in]
         dev_in = [torch.empty_like(t) for t in host_in]
         out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
@@ -330,7 +330,7 @@ def run_ours(args, rank, world, local_rank):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "roofline": roofline,
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "impl": "ours"}
     line["us_per_step"] = ms_per_step * 1e3
-    if wl == "decode_b60" and world == 1 and not args.no_cpu_baseline:
+    if wl == "decode_b60" and world == 1 and not args.no_cpu_baseline and not args.profile:
         line["cpu_baseline"] = cpu_baseline_decode()
     if extra:
         line["extra"] = extra
@@ -421,7 +421,11 @@ def main():
     ap.add_argument("--workload", default="decode_b60",
                     choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
+    ap.add_argument("--batch", type=int, default=0,
+                    help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="for runs under a profiler: no CPU baseline, no end-to-end leg, no clock-sampling repeats")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

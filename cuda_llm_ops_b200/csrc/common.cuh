@@ -20,6 +20,7 @@ enum : int {
     SITE_DECODE_FULL = 1,
     SITE_DECODE_EMPTY = 2,
     SITE_DECODE_DRAIN = 3,
+    SITE_DECODE_ISSUE = 4,
     SITE_PREFILL_BASE = 16,
 };
 

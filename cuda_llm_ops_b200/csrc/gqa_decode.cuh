@@ -40,7 +40,7 @@ constexpr int kMergeBufs = 4;
 constexpr int kRows = 16;                    // query-head rows per unit (MMA M)
 constexpr int kPW = kD + 2;                  // packed partial row width
 constexpr int kSlotFloats = kRows * kPW;     // one partial slot in the workspace
-constexpr int kSmemBytes = kStages * kStageBytes + kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8 + 16 + 1024;
+constexpr int kSmemBytes = kStages * kStageBytes + kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -73,6 +73,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t bar_base = base + kStages * kStageBytes + kMergeBufs * kMergeFloats * 4;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kStages * kStageBytes +
                                                                kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8);
+    // number of tiles the producer has issued so far.  A consumer looks at a stage's full barrier only once
+    // ITS tile has been issued: the stages are shared by all consumer warps, and a parity wait placed two
+    // phases early would be satisfied by the wrong phase.
+    volatile long long* issued = reinterpret_cast<volatile long long*>(
+        gen_base + kStages * kStageBytes + kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8 + 16);
     auto full_bar = [&](int s) { return bar_base + s * 8; };
     auto empty_bar = [&](int s) { return bar_base + (kStages + s) * 8; };
 
@@ -86,6 +91,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             mbar_init(empty_bar(s), 1);
         }
         *abort_flag = 0;
+        *issued = 0;
         fence_mbar_init();
     }
     __syncthreads();
@@ -113,6 +119,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 tma_load_4d(dst + kHalfBytes, &tm_k, full_bar(slot), 64, c1, c2, b);
                 tma_load_4d(dst + 2 * kHalfBytes, &tm_v, full_bar(slot), 0, c1, c2, b);
                 tma_load_4d(dst + 3 * kHalfBytes, &tm_v, full_bar(slot), 64, c1, c2, b);
+                __threadfence_block();
+                *issued = it + 1;
             }
             if (*abort_flag) {
                 // a wait gave up somewhere: make sure no copy is still landing when the block retires
@@ -174,7 +182,17 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             const long long it = t - lo;
             const int slot = static_cast<int>(it % kStages);
             const uint32_t use = static_cast<uint32_t>(it / kStages);
+            if (*issued <= it) {
+                const long long t0 = clock64();
+                while (*issued <= it && !*abort_flag) {
+                    if (clock64() - t0 > kWaitLimitCycles) {
+                        *abort_flag = 1;
+                        record_timeout(SITE_DECODE_ISSUE, slot);
+                    }
+                }
+            }
             mbar_wait(full_bar(slot), use & 1u, abort_flag, SITE_DECODE_FULL, slot);
+            __syncwarp();
             const uint32_t kb = stage_base + slot * kStageBytes;
             const uint32_t vb = kb + 2 * kHalfBytes;
             const int tok0 = static_cast<int>(t - unit_lo) * kTok;

@@ -358,6 +358,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
             mbar_wait(bar_s_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_S_FULL, j);
+            __syncwarp();
             tc_fence_after();
             float x[128];
             tmem_ld128_wait(s_addr, x);
@@ -393,6 +394,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (j > 0) {
                     alpha = fast_exp2(m - m_new);
                     mbar_wait(bar_o_full(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
+                    __syncwarp();
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
@@ -430,6 +432,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
         // epilogue: O / l -> bf16, lse = m + log(l)
         mbar_wait(bar_o_full(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
+        __syncwarp();
         tc_fence_after();
         const float inv_l = 1.f / l;
         const bool row_ok = qi < p.Sq;
