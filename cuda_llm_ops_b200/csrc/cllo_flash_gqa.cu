@@ -129,7 +129,7 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
     decode::decode_splitkv_kernel<<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(tm_k, tm_v, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     if (plan.needs_merge) {
-        decode::decode_merge_kernel<<<static_cast<unsigned>(plan.units), decode::kD, 0, st>>>(p);
+        decode::decode_merge_kernel<<<static_cast<unsigned>(plan.units), decode::kMergeThreads, 0, st>>>(p);
         CLLO_CUDA_TRY(cudaGetLastError());
     }
     return CLLO_OK;

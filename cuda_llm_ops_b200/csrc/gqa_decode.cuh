@@ -7,14 +7,17 @@
 // whole units plus at most one partial unit at each end of its range.
 //
 // Inside a worker.  One producer warp issues TMA tile loads (K and V, 64 tokens x 128 dims each,
-// 128-byte swizzled, 32 KB per stage) into a 5-stage ring guarded by full/empty mbarriers.  Eight
-// consumer warps take stages round-robin.  Each consumer warp computes, for ITS 64 tokens and ALL
-// query heads of the unit (padded to 16 rows): S = Q K^T with mma.sync m16n8k16 (K fragments via
-// ldmatrix), an online-softmax update of its private running (m, l, O) with quad shuffles, and
-// O += P V (V fragments via ldmatrix.trans, P fed straight from the accumulator registers).  There
-// is no block-wide barrier in the streaming loop.  At the end of a unit the eight private states are
-// merged pairwise through shared memory (log-sum-exp algebra), and warp 0 writes either the final
-// bf16 output (unit entirely inside this worker) or an fp32 partial (O, m, l) to the workspace.
+// 128-byte swizzled, 32 KB per stage) into a 6-stage ring guarded by full/empty mbarriers.  The eight
+// consumer warps form two groups of four; the groups take stages alternately and the four warps of a
+// group split a stage's 64 tokens 16 apiece, so a stage is held for a quarter of the time one warp
+// would need and goes back to the producer (and to the memory system) sooner.  For ITS 16 tokens and
+// ALL query heads of the unit (padded to 16 rows) a warp computes S = Q K^T with mma.sync m16n8k16
+// (K fragments via ldmatrix), an online-softmax update of its private running (m, l, O) with quad
+// shuffles (O is rescaled only when a maximum actually grew), and O += P V (V fragments via
+// ldmatrix.trans, P fed straight from the accumulator registers).  There is no block-wide barrier in
+// the streaming loop.  At the end of a unit the eight private states are merged through shared memory
+// (log-sum-exp algebra, fixed summation order) and every warp writes its share of either the final
+// bf16 output (unit entirely inside this worker) or an fp32 partial (O, m, l) in the workspace.
 //
 // Second pass.  decode_merge_kernel visits every unit that was cut by a worker boundary and merges
 // its partials:  m* = max m_i,  O = sum e^(m_i-m*) O_i / sum e^(m_i-m*) l_i.
@@ -29,20 +32,29 @@ namespace cllo {
 namespace decode {
 
 constexpr int kD = 128;
-constexpr int kTok = 64;
-constexpr int kStages = 5;
-constexpr int kConsumerWarps = 8;
+constexpr int kTok = 64;                     // tokens per stage
+constexpr int kStages = 6;
+constexpr int kGroups = 2;                   // consumer groups; kStages must be a multiple of it so that a
+                                             // stage buffer is always drained by the same group, in order
+constexpr int kWarpsPerGroup = 4;
+constexpr int kSubTok = kTok / kWarpsPerGroup;  // tokens per warp per stage
+constexpr int kConsumerWarps = kGroups * kWarpsPerGroup;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kHalfBytes = kTok * 128;       // [64 tokens][64 dims] bf16
 constexpr int kStageBytes = 4 * kHalfBytes;  // K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127
-constexpr int kMergeFloats = 68 * 32;        // per lane: 64 O values, m0, m1, l0, l1
-constexpr int kMergeBufs = 4;
+constexpr int kStatFloats = kConsumerWarps * 4 * 32;    // per warp, per lane: m0, m1, l0, l1
+constexpr int kXchgFloats = kConsumerWarps * 16 * 32;   // per warp, per lane: 16 of the 64 O values
 constexpr int kRows = 16;                    // query-head rows per unit (MMA M)
 constexpr int kPW = kD + 2;                  // packed partial row width
 constexpr int kSlotFloats = kRows * kPW;     // one partial slot in the workspace
-constexpr int kSmemBytes = kStages * kStageBytes + kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8 + 32 + 1024;
+constexpr int kSmemStat = kStages * kStageBytes;
+constexpr int kSmemXchg = kSmemStat + kStatFloats * 4;
+constexpr int kSmemBar = kSmemXchg + kXchgFloats * 4;
+constexpr int kSmemBytes = kSmemBar + 2 * kStages * 8 + 16 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+static_assert(kStages % kGroups == 0, "a stage buffer must always belong to the same consumer group");
+static_assert(kSubTok == 16, "one PV k-step per warp per stage");
 
 struct Params {
     const __nv_bfloat16* q;
@@ -69,15 +81,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t stage_base = base;
-    float* merge = reinterpret_cast<float*>(gen_base + kStages * kStageBytes);
-    const uint32_t bar_base = base + kStages * kStageBytes + kMergeBufs * kMergeFloats * 4;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kStages * kStageBytes +
-                                                               kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8);
-    // number of tiles the producer has issued so far.  A consumer looks at a stage's full barrier only once
-    // ITS tile has been issued: the stages are shared by all consumer warps, and a parity wait placed two
-    // phases early would be satisfied by the wrong phase.
-    volatile long long* issued = reinterpret_cast<volatile long long*>(
-        gen_base + kStages * kStageBytes + kMergeBufs * kMergeFloats * 4 + 2 * kStages * 8 + 16);
+    float* stat = reinterpret_cast<float*>(gen_base + kSmemStat);
+    float* xchg = reinterpret_cast<float*>(gen_base + kSmemXchg);
+    const uint32_t bar_base = base + kSmemBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + 2 * kStages * 8);
     auto full_bar = [&](int s) { return bar_base + s * 8; };
     auto empty_bar = [&](int s) { return bar_base + (kStages + s) * 8; };
 
@@ -88,10 +95,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), kWarpsPerGroup);
         }
         *abort_flag = 0;
-        *issued = 0;
         fence_mbar_init();
     }
     __syncthreads();
@@ -119,8 +125,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 tma_load_4d(dst + kHalfBytes, &tm_k, full_bar(slot), 64, c1, c2, b);
                 tma_load_4d(dst + 2 * kHalfBytes, &tm_v, full_bar(slot), 0, c1, c2, b);
                 tma_load_4d(dst + 3 * kHalfBytes, &tm_v, full_bar(slot), 64, c1, c2, b);
-                __threadfence_block();
-                *issued = it + 1;
             }
             if (*abort_flag) {
                 // a wait gave up somewhere: make sure no copy is still landing when the block retires
@@ -143,6 +147,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     // -------------------------------- consumers --------------------------------
     const int g = lane >> 2, tig = lane & 3;
+    const int grp = warp / kWarpsPerGroup, sub = warp % kWarpsPerGroup;
     const long long u_first = lo / p.n_t, u_last = (hi - 1) / p.n_t;
 
 #pragma unroll 1
@@ -176,188 +181,183 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-        const long long first = seg_lo + ((static_cast<long long>(warp) - (seg_lo - lo)) % 8 + 8) % 8;
+        // this group's tiles of the segment: local index (t - lo) congruent to grp modulo kGroups
+        const long long first = seg_lo + ((static_cast<long long>(grp) - (seg_lo - lo)) % kGroups + kGroups) % kGroups;
 #pragma unroll 1
-        for (long long t = first; t < seg_hi; t += kConsumerWarps) {
+        for (long long t = first; t < seg_hi; t += kGroups) {
             const long long it = t - lo;
             const int slot = static_cast<int>(it % kStages);
             const uint32_t use = static_cast<uint32_t>(it / kStages);
-            if (*issued <= it) {
-                const long long t0 = clock64();
-                while (*issued <= it && !*abort_flag) {
-                    if (clock64() - t0 > kWaitLimitCycles) {
-                        *abort_flag = 1;
-                        record_timeout(SITE_DECODE_ISSUE, slot);
-                    }
-                }
-            }
             mbar_wait(full_bar(slot), use & 1u, abort_flag, SITE_DECODE_FULL, slot);
             __syncwarp();
             const uint32_t kb = stage_base + slot * kStageBytes;
             const uint32_t vb = kb + 2 * kHalfBytes;
-            const int tok0 = static_cast<int>(t - unit_lo) * kTok;
-            const int valid = (p.S - tok0) < kTok ? (p.S - tok0) : kTok;
+            const int tok0 = static_cast<int>(t - unit_lo) * kTok + sub * kSubTok;  // first token of this warp
+            const int valid = p.S - tok0;  // tokens of this warp's 16 that exist (may be <= 0 or >= 16)
 
-            // ---- S = Q K^T  (16 x 64) ----
-            float s[8][4];
+            if (valid > 0) {
+                // ---- S = Q K^T  (16 heads x 16 tokens) ----
+                float s[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-                const uint32_t row_off = static_cast<uint32_t>(nt * 8 + (lane & 7)) * 128u;
+                for (int nt = 0; nt < 2; ++nt) {
+                    s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+                    const uint32_t row_off = static_cast<uint32_t>(sub * kSubTok + nt * 8 + (lane & 7)) * 128u;
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t chunk = static_cast<uint32_t>((kk & 1) * 4 + (lane >> 3));
-                    const uint32_t addr = kb + (kk >> 1) * kHalfBytes + row_off + ((chunk ^ (lane & 7)) << 4);
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(addr, b0, b1, b2, b3);
-                    mma_bf16_16816(s[nt], qf[2 * kk], b0, b1);
-                    mma_bf16_16816(s[nt], qf[2 * kk + 1], b2, b3);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint32_t chunk = static_cast<uint32_t>((kk & 1) * 4 + (lane >> 3));
+                        const uint32_t addr = kb + (kk >> 1) * kHalfBytes + row_off + ((chunk ^ (lane & 7)) << 4);
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(addr, b0, b1, b2, b3);
+                        mma_bf16_16816(s[nt], qf[2 * kk], b0, b1);
+                        mma_bf16_16816(s[nt], qf[2 * kk + 1], b2, b3);
+                    }
                 }
-            }
 
-            // ---- online softmax on this warp's private state ----
-            float mx0 = -INFINITY, mx1 = -INFINITY;
+                // ---- online softmax on this warp's private state ----
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+                for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
-                if (valid < kTok) {
-                    const int c = nt * 8 + tig * 2;
-                    if (c >= valid) s[nt][0] = s[nt][2] = -INFINITY;
-                    if (c + 1 >= valid) s[nt][1] = s[nt][3] = -INFINITY;
+                    for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
+                    if (valid < kSubTok) {
+                        const int c = nt * 8 + tig * 2;
+                        if (c >= valid) s[nt][0] = s[nt][2] = -INFINITY;
+                        if (c + 1 >= valid) s[nt][1] = s[nt][3] = -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                    mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
                 }
-                mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-                mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
-            }
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
-            m0 = mn0;
-            m1 = mn1;
-            float sum0 = 0.f, sum1 = 0.f;
-            uint32_t pa[4][4];
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
+                    // a maximum grew somewhere in the warp: bring O and l to the new reference
+                    const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+                    l0 *= a0;
+                    l1 *= a1;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const float p0 = fast_exp2(s[nt][0] - mn0), p1 = fast_exp2(s[nt][1] - mn0);
-                const float p2 = fast_exp2(s[nt][2] - mn1), p3 = fast_exp2(s[nt][3] - mn1);
-                sum0 += p0 + p1;
-                sum1 += p2 + p3;
-                pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(p0, p1);
-                pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
-            }
-            l0 = l0 * a0 + sum0;
-            l1 = l1 * a1 + sum1;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                o[i][0] *= a0;
-                o[i][1] *= a0;
-                o[i][2] *= a1;
-                o[i][3] *= a1;
-            }
+                    for (int i = 0; i < 16; ++i) {
+                        o[i][0] *= a0;
+                        o[i][1] *= a0;
+                        o[i][2] *= a1;
+                        o[i][3] *= a1;
+                    }
+                    m0 = mn0;
+                    m1 = mn1;
+                }
+                uint32_t pa[4];
+                {
+                    const float p00 = fast_exp2(s[0][0] - m0), p01 = fast_exp2(s[0][1] - m0);
+                    const float p02 = fast_exp2(s[0][2] - m1), p03 = fast_exp2(s[0][3] - m1);
+                    const float p10 = fast_exp2(s[1][0] - m0), p11 = fast_exp2(s[1][1] - m0);
+                    const float p12 = fast_exp2(s[1][2] - m1), p13 = fast_exp2(s[1][3] - m1);
+                    l0 += (p00 + p01) + (p10 + p11);
+                    l1 += (p02 + p03) + (p12 + p13);
+                    pa[0] = pack_bf16x2(p00, p01);
+                    pa[1] = pack_bf16x2(p02, p03);
+                    pa[2] = pack_bf16x2(p10, p11);
+                    pa[3] = pack_bf16x2(p12, p13);
+                }
 
-            // ---- O += P V  (16 x 128) ----
-#pragma unroll
-            for (int kt = 0; kt < 4; ++kt) {
-                const uint32_t tok = static_cast<uint32_t>(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8);
+                // ---- O += P V  (16 heads x 128 dims, one 16-token k-step) ----
+                const uint32_t tok = static_cast<uint32_t>(sub * kSubTok + (lane & 7) + ((lane >> 3) & 1) * 8);
 #pragma unroll
                 for (int np = 0; np < 8; ++np) {
                     const uint32_t chunk = static_cast<uint32_t>((np & 3) * 2 + (lane >> 4));
                     const uint32_t addr = vb + (np >> 2) * kHalfBytes + tok * 128u + ((chunk ^ (tok & 7u)) << 4);
                     uint32_t b0, b1, b2, b3;
                     ldmatrix_x4_trans(addr, b0, b1, b2, b3);
-                    mma_bf16_16816(o[2 * np], pa[kt], b0, b1);
-                    mma_bf16_16816(o[2 * np + 1], pa[kt], b2, b3);
+                    mma_bf16_16816(o[2 * np], pa, b0, b1);
+                    mma_bf16_16816(o[2 * np + 1], pa, b2, b3);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(slot));
         }
 
-        // ---- merge the eight private states (pairwise tree through shared memory) ----
-#pragma unroll 1
-        for (int st = 1; st < kConsumerWarps; st <<= 1) {
-            const bool writer = (warp % (2 * st)) == st;
-            const bool reader = (warp % (2 * st)) == 0;
-            float* buf = merge + (warp / (2 * st)) * kMergeFloats;
-            if (writer) {
+        // ---- merge the eight private states ----
+        // 1. publish (m, l); everyone derives the common maximum, its own rescale factor and the total l
+        stat[(warp * 4 + 0) * 32 + lane] = m0;
+        stat[(warp * 4 + 1) * 32 + lane] = m1;
+        stat[(warp * 4 + 2) * 32 + lane] = l0;
+        stat[(warp * 4 + 3) * 32 + lane] = l1;
+        named_bar_sync(1, kConsumerWarps * 32);
+        float ms0 = -INFINITY, ms1 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) buf[i * 32 + lane] = o[i >> 2][i & 3];
-                buf[64 * 32 + lane] = m0;
-                buf[65 * 32 + lane] = m1;
-                buf[66 * 32 + lane] = l0;
-                buf[67 * 32 + lane] = l1;
+        for (int sw = 0; sw < kConsumerWarps; ++sw) {
+            ms0 = fmaxf(ms0, stat[(sw * 4 + 0) * 32 + lane]);
+            ms1 = fmaxf(ms1, stat[(sw * 4 + 1) * 32 + lane]);
+        }
+        float lt0 = 0.f, lt1 = 0.f;
+#pragma unroll
+        for (int sw = 0; sw < kConsumerWarps; ++sw) {
+            const float wm0 = stat[(sw * 4 + 0) * 32 + lane], wm1 = stat[(sw * 4 + 1) * 32 + lane];
+            lt0 += (wm0 == -INFINITY) ? 0.f : stat[(sw * 4 + 2) * 32 + lane] * fast_exp2(wm0 - ms0);
+            lt1 += (wm1 == -INFINITY) ? 0.f : stat[(sw * 4 + 3) * 32 + lane] * fast_exp2(wm1 - ms1);
+        }
+        lt0 += __shfl_xor_sync(0xffffffffu, lt0, 1);
+        lt0 += __shfl_xor_sync(0xffffffffu, lt0, 2);
+        lt1 += __shfl_xor_sync(0xffffffffu, lt1, 1);
+        lt1 += __shfl_xor_sync(0xffffffffu, lt1, 2);
+        const float f0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - ms0);
+        const float f1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - ms1);
+        // 2. four rounds; in each, every warp posts 16 of its 64 (rescaled) O values and then sums, over
+        //    the eight warps in fixed order, the two values it owns.  Warp w ends up owning, for the row
+        //    half (w & 1) and the n-tiles congruent to (w >> 1) modulo 4, the two columns of its lanes.
+        float acc[4][2];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int idx = r * 16 + i;
+                xchg[(warp * 16 + i) * 32 + lane] = o[idx >> 2][idx & 3] * ((idx & 2) ? f1 : f0);
             }
             named_bar_sync(1, kConsumerWarps * 32);
-            if (reader) {
-                const float om0 = buf[64 * 32 + lane], om1 = buf[65 * 32 + lane];
-                const float ol0 = buf[66 * 32 + lane], ol1 = buf[67 * 32 + lane];
-                const float mn0 = fmaxf(m0, om0), mn1 = fmaxf(m1, om1);
-                const float sa0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mn0);
-                const float sa1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mn1);
-                const float sb0 = (om0 == -INFINITY) ? 0.f : fast_exp2(om0 - mn0);
-                const float sb1 = (om1 == -INFINITY) ? 0.f : fast_exp2(om1 - mn1);
-                l0 = l0 * sa0 + ol0 * sb0;
-                l1 = l1 * sa1 + ol1 * sb1;
-                m0 = mn0;
-                m1 = mn1;
+            float a = 0.f, c = 0.f;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float other = buf[i * 32 + lane];
-                    const bool hi_row = (i & 2) != 0;
-                    o[i >> 2][i & 3] = o[i >> 2][i & 3] * (hi_row ? sa1 : sa0) + other * (hi_row ? sb1 : sb0);
-                }
+            for (int sw = 0; sw < kConsumerWarps; ++sw) {
+                a += xchg[(sw * 16 + 2 * warp) * 32 + lane];
+                c += xchg[(sw * 16 + 2 * warp + 1) * 32 + lane];
             }
+            acc[r][0] = a;
+            acc[r][1] = c;
             named_bar_sync(1, kConsumerWarps * 32);
         }
 
-        // ---- warp 0 owns the merged result ----
-        if (warp == 0) {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-            l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        // ---- every warp writes its share ----
+        {
+            const int hrow = warp & 1;             // 0: row g, 1: row g + 8
+            const int row = g + 8 * hrow;
+            const float mrow = hrow ? ms1 : ms0;
+            const float lrow = hrow ? lt1 : lt0;
             const bool whole = (seg_lo == unit_lo) && (seg_hi == unit_hi);
-            if (whole && p.partial_out == nullptr) {
-                const float i0 = 1.f / l0, i1 = 1.f / l1;
+            if (row < rows) {
+                if (whole && p.partial_out == nullptr) {
+                    const float inv = 1.f / lrow;
 #pragma unroll
-                for (int nt = 0; nt < 16; ++nt) {
-                    const int col = nt * 8 + tig * 2;
-                    if (g < rows)
-                        *reinterpret_cast<uint32_t*>(p.o + (head0 + g) * kD + col) =
-                            pack_bf16x2(o[nt][0] * i0, o[nt][1] * i0);
-                    if (g + 8 < rows)
-                        *reinterpret_cast<uint32_t*>(p.o + (head0 + g + 8) * kD + col) =
-                            pack_bf16x2(o[nt][2] * i1, o[nt][3] * i1);
-                }
-            } else {
-                float* d0;
-                float* d1;
-                if (whole) {
-                    d0 = p.partial_out + (head0 + g) * kPW;
-                    d1 = p.partial_out + (head0 + g + 8) * kPW;
-                } else {
-                    const int which = (u == u_first) ? 0 : 1;
-                    float* slot_base = p.ws + (w * 2 + which) * kSlotFloats;
-                    d0 = slot_base + g * kPW;
-                    d1 = slot_base + (g + 8) * kPW;
-                }
-#pragma unroll
-                for (int nt = 0; nt < 16; ++nt) {
-                    const int col = nt * 8 + tig * 2;
-                    if (g < rows) *reinterpret_cast<float2*>(d0 + col) = make_float2(o[nt][0], o[nt][1]);
-                    if (g + 8 < rows) *reinterpret_cast<float2*>(d1 + col) = make_float2(o[nt][2], o[nt][3]);
-                }
-                if (tig == 0) {
-                    if (g < rows) {
-                        d0[kD] = m0 * kLn2;
-                        d0[kD + 1] = l0;
+                    for (int r = 0; r < 4; ++r) {
+                        const int col = (r * 4 + (warp >> 1)) * 8 + tig * 2;
+                        *reinterpret_cast<uint32_t*>(p.o + (head0 + row) * kD + col) =
+                            pack_bf16x2(acc[r][0] * inv, acc[r][1] * inv);
                     }
-                    if (g + 8 < rows) {
-                        d1[kD] = m1 * kLn2;
-                        d1[kD + 1] = l1;
+                } else {
+                    float* dst;
+                    if (whole) {
+                        dst = p.partial_out + (head0 + row) * kPW;
+                    } else {
+                        const int which = (u == u_first) ? 0 : 1;
+                        dst = p.ws + (w * 2 + which) * kSlotFloats + row * kPW;
+                    }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int col = (r * 4 + (warp >> 1)) * 8 + tig * 2;
+                        *reinterpret_cast<float2*>(dst + col) = make_float2(acc[r][0], acc[r][1]);
+                    }
+                    if (tig == 0 && (warp >> 1) == 0) {
+                        dst[kD] = mrow * kLn2;
+                        dst[kD + 1] = lrow;
                     }
                 }
             }
@@ -365,8 +365,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
 }
 
-// Second pass over the units that a worker boundary cut.  grid = units, block = 128 (one thread per dim).
-__global__ void __launch_bounds__(kD) decode_merge_kernel(const Params p) {
+// Second pass over the units that a worker boundary cut.  grid = units, block = 512: thread (row, 4 dims).
+constexpr int kMergeThreads = kRows * (kD / 4);
+__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Params p) {
     const long long u = blockIdx.x;
     const long long t_first = u * p.n_t, t_last = t_first + p.n_t - 1;
     const long long w_lo = worker_of_tile(t_first, p.T, p.W), w_hi = worker_of_tile(t_last, p.T, p.W);
@@ -377,31 +378,43 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const Params p) {
     const int rows = (p.G - gblk * kRows) < kRows ? (p.G - gblk * kRows) : kRows;
     const long long head0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * p.G + gblk * kRows;
     const int which_lo = (worker_lo(w_lo, p.T, p.W) == t_first) ? 0 : 1;
-    const int d = threadIdx.x;
-    for (int r = 0; r < rows; ++r) {
-        float mstar = -INFINITY;
-        for (long long w = w_lo; w <= w_hi; ++w) {
-            const float* row = p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
-            if (row[kD + 1] > 0.f) mstar = fmaxf(mstar, row[kD]);
+    const int r = threadIdx.x >> 5, c4 = (threadIdx.x & 31) * 4;
+    if (r >= rows) return;
+    auto row_ptr = [&](long long w) {
+        return p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
+    };
+    float mstar = -INFINITY;
+    for (long long w = w_lo; w <= w_hi; ++w) {
+        const float* row = row_ptr(w);
+        if (row[kD + 1] > 0.f) mstar = fmaxf(mstar, row[kD]);
+    }
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
+    for (long long w = w_lo; w <= w_hi; ++w) {
+        const float* row = row_ptr(w);
+        const float l = row[kD + 1];
+        const float wgt = l > 0.f ? __expf(row[kD] - mstar) : 0.f;
+        const float2 x = *reinterpret_cast<const float2*>(row + c4);
+        const float2 y = *reinterpret_cast<const float2*>(row + c4 + 2);
+        a0 += wgt * x.x;
+        a1 += wgt * x.y;
+        a2 += wgt * y.x;
+        a3 += wgt * y.y;
+        lsum += wgt * l;
+    }
+    if (p.partial_out) {
+        float* dst = p.partial_out + (head0 + r) * kPW;
+        *reinterpret_cast<float2*>(dst + c4) = make_float2(a0, a1);
+        *reinterpret_cast<float2*>(dst + c4 + 2) = make_float2(a2, a3);
+        if (c4 == 0) {
+            dst[kD] = mstar;
+            dst[kD + 1] = lsum;
         }
-        float acc = 0.f, lsum = 0.f;
-        for (long long w = w_lo; w <= w_hi; ++w) {
-            const float* row = p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
-            const float l = row[kD + 1];
-            const float wgt = l > 0.f ? __expf(row[kD] - mstar) : 0.f;
-            acc += wgt * row[d];
-            lsum += wgt * l;
-        }
-        if (p.partial_out) {
-            float* dst = p.partial_out + (head0 + r) * kPW;
-            dst[d] = acc;
-            if (d == 0) {
-                dst[kD] = mstar;
-                dst[kD + 1] = lsum;
-            }
-        } else {
-            p.o[(head0 + r) * kD + d] = __float2bfloat16(lsum > 0.f ? acc / lsum : 0.f);
-        }
+    } else {
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        uint2 pk;
+        pk.x = pack_bf16x2(a0 * inv, a1 * inv);
+        pk.y = pack_bf16x2(a2 * inv, a3 * inv);
+        *reinterpret_cast<uint2*>(p.o + (head0 + r) * kD + c4) = pk;
     }
 }
 
