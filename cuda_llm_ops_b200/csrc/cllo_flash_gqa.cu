@@ -129,8 +129,19 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
     decode::decode_splitkv_kernel<<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(tm_k, tm_v, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     if (plan.needs_merge) {
-        decode::decode_merge_kernel<<<static_cast<unsigned>(plan.units), decode::kMergeThreads, 0, st>>>(p);
-        CLLO_CUDA_TRY(cudaGetLastError());
+        // launched with programmatic stream serialization: its blocks become resident while the main
+        // kernel drains and start the moment that grid has completed
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(plan.units));
+        cfg.blockDim = dim3(decode::kMergeThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel, p));
     }
     return CLLO_OK;
 }

@@ -101,6 +101,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         fence_mbar_init();
     }
     __syncthreads();
+    // the merge pass may become resident now; it waits for this whole grid before it reads anything
+    pdl_launch_dependents();
     if (lo >= hi) return;
 
     if (warp == kConsumerWarps) {
@@ -108,23 +110,43 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         if (lane == 0) {
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            for (long long t = lo; t < hi; ++t) {
-                const long long it = t - lo;
-                const int slot = static_cast<int>(it % kStages);
-                const uint32_t use = static_cast<uint32_t>(it / kStages);
-                mbar_wait(empty_bar(slot), (use & 1u) ^ 1u, abort_flag, SITE_DECODE_EMPTY, slot);
-                const long long u = t / p.n_t;
-                const int s0 = static_cast<int>(t - u * p.n_t) * kTok;
-                const int kvh = static_cast<int>((u / p.n_gblk) % p.Hkv);
-                const int b = static_cast<int>(u / (static_cast<long long>(p.n_gblk) * p.Hkv));
-                const int c1 = p.kv_layout == CLLO_KV_BSHD ? kvh : s0;
-                const int c2 = p.kv_layout == CLLO_KV_BSHD ? s0 : kvh;
+            // all indices advance incrementally: this one thread paces the whole block, so its loop carries
+            // no division
+            long long u = lo / p.n_t;
+            int tile_in_unit = static_cast<int>(lo - u * p.n_t);
+            int gblk = static_cast<int>(u % p.n_gblk);
+            int kvh = static_cast<int>((u / p.n_gblk) % p.Hkv);
+            int b = static_cast<int>(u / (static_cast<long long>(p.n_gblk) * p.Hkv));
+            int slot = 0;
+            uint32_t phase = 0;
+            const int n_tiles = static_cast<int>(hi - lo);
+            const bool bshd = p.kv_layout == CLLO_KV_BSHD;
+#pragma unroll 1
+            for (int it = 0; it < n_tiles; ++it) {
+                mbar_wait(empty_bar(slot), phase ^ 1u, abort_flag, SITE_DECODE_EMPTY, slot);
+                const int s0 = tile_in_unit * kTok;
+                const int c1 = bshd ? kvh : s0;
+                const int c2 = bshd ? s0 : kvh;
                 const uint32_t dst = stage_base + slot * kStageBytes;
                 mbar_arrive_expect_tx(full_bar(slot), kStageBytes);
                 tma_load_4d(dst, &tm_k, full_bar(slot), 0, c1, c2, b);
                 tma_load_4d(dst + kHalfBytes, &tm_k, full_bar(slot), 64, c1, c2, b);
                 tma_load_4d(dst + 2 * kHalfBytes, &tm_v, full_bar(slot), 0, c1, c2, b);
                 tma_load_4d(dst + 3 * kHalfBytes, &tm_v, full_bar(slot), 64, c1, c2, b);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+                if (++tile_in_unit == p.n_t) {
+                    tile_in_unit = 0;
+                    if (++gblk == p.n_gblk) {
+                        gblk = 0;
+                        if (++kvh == p.Hkv) {
+                            kvh = 0;
+                            ++b;
+                        }
+                    }
+                }
             }
             if (*abort_flag) {
                 // a wait gave up somewhere: make sure no copy is still landing when the block retires
@@ -185,8 +207,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const long long first = seg_lo + ((static_cast<long long>(grp) - (seg_lo - lo)) % kGroups + kGroups) % kGroups;
 #pragma unroll 1
         for (long long t = first; t < seg_hi; t += kGroups) {
-            const long long it = t - lo;
-            const int slot = static_cast<int>(it % kStages);
+            const int it = static_cast<int>(t - lo);
+            const int slot = it % kStages;
             const uint32_t use = static_cast<uint32_t>(it / kStages);
             mbar_wait(full_bar(slot), use & 1u, abort_flag, SITE_DECODE_FULL, slot);
             __syncwarp();
@@ -380,19 +402,24 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Param
     const int which_lo = (worker_lo(w_lo, p.T, p.W) == t_first) ? 0 : 1;
     const int r = threadIdx.x >> 5, c4 = (threadIdx.x & 31) * 4;
     if (r >= rows) return;
+    pdl_wait_prior_grid();
     auto row_ptr = [&](long long w) {
         return p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
     };
+    // branch-free bodies so that the loads of several pieces are in flight together
     float mstar = -INFINITY;
+#pragma unroll 4
     for (long long w = w_lo; w <= w_hi; ++w) {
-        const float* row = row_ptr(w);
-        if (row[kD + 1] > 0.f) mstar = fmaxf(mstar, row[kD]);
+        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(w) + kD);
+        mstar = fmaxf(mstar, ml.y > 0.f ? ml.x : -INFINITY);
     }
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
+#pragma unroll 4
     for (long long w = w_lo; w <= w_hi; ++w) {
         const float* row = row_ptr(w);
-        const float l = row[kD + 1];
-        const float wgt = l > 0.f ? __expf(row[kD] - mstar) : 0.f;
+        const float2 ml = *reinterpret_cast<const float2*>(row + kD);
+        const float l = ml.y;
+        const float wgt = l > 0.f ? __expf(ml.x - mstar) : 0.f;
         const float2 x = *reinterpret_cast<const float2*>(row + c4);
         const float2 y = *reinterpret_cast<const float2*>(row + c4 + 2);
         a0 += wgt * x.x;
@@ -467,6 +494,7 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     if (W > p.T) W = p.T;
     if (W < 1) W = 1;
     p.W = static_cast<int>(W);
+    if (p.T / W + 1 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // a worker's tile count is a 32-bit loop index
     plan->ws_bytes = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
     plan->needs_merge = false;
     for (long long w = 1; w < W; ++w)
