@@ -8,6 +8,15 @@
 
 using namespace cllo;
 
+// Scratch for cllo_gqa_decode_bf16_noalloc: room for the split-KV partials of up to
+// CLLO_NOALLOC_MAX_WORKERS persistent blocks.  It lives in the library image, so every GPU that loads
+// the library carries these ~2.5 MiB until the process exits.  Host code must never hand this NAME to
+// a kernel: on the host it is only a stand-in, the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[
+    static_cast<size_t>(CLLO_NOALLOC_MAX_WORKERS) * 2 * decode::kSlotFloats * sizeof(float)];
+static void* g_noalloc_ptr[kMaxDevices];  // device address of the array, looked up once per device
+static std::mutex g_noalloc_mutex;
+
 extern "C" {
 
 int cllo_version(void) { return 100; }
@@ -160,6 +169,32 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
     return prefill::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
+}
+
+// Decode for callers that may not allocate device memory: the partials go to the fixed array above.
+int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, float scale, void* o, int B, int S,
+                                 int Hq, int Hkv, int D, int kv_layout, int num_workers, void* stream) {
+    if (num_workers > CLLO_NOALLOC_MAX_WORKERS) return CLLO_E_WORKSPACE;  // would not fit the fixed scratch
+    int dev = 0;
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di, &dev);
+    if (rc != CLLO_OK) return rc;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ptr[dev]) {
+            // set-up, once per device, with that device current (current_device_info asked which it is)
+            void* ptr = nullptr;
+            CLLO_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+            if (!ptr) return CLLO_E_CUDA;
+            g_noalloc_ptr[dev] = ptr;
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    if (num_workers <= 0)
+        num_workers = di->sm_count < CLLO_NOALLOC_MAX_WORKERS ? di->sm_count : CLLO_NOALLOC_MAX_WORKERS;
+    return cllo_gqa_decode_bf16(q, k, v, scale, o, scratch, sizeof(g_noalloc_scratch), B, S, Hq, Hkv, D, kv_layout,
+                                num_workers, nullptr, stream);
 }
 
 // Source-compatibility path for upstream's C++ launcher signature (no workspace argument): use the

@@ -85,6 +85,33 @@ int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, flo
                                 float* o_intermediate, int B, int S, int Hq, int Hkv, int D);
 
 /*
+ * Decode without any allocation, by the caller or by the library.  (No counterpart upstream: upstream's
+ * launcher takes its scratch from the caller.)
+ *
+ * Some hosts of this library cannot provide a workspace: an inference server that has handed every byte
+ * of device memory to its KV-cache pool and forbids plugins to allocate; a latency-critical decode loop
+ * that cannot afford the device-wide synchronisation a cudaMalloc/cudaFree implies; a caller that only
+ * receives the tensors' pointers.  For them this variant keeps the split-KV partials in a fixed
+ * __device__ array inside the library (CLLO_NOALLOC_MAX_WORKERS * 16,640 bytes, about 2.5 MiB, resident
+ * on every GPU that loads the library until the process exits).  It calls neither cudaMalloc nor
+ * cudaFree nor any allocating routine.
+ *
+ * Same arguments and results as cllo_gqa_decode_bf16 without workspace and partial_out.  Limits:
+ *   - num_workers > CLLO_NOALLOC_MAX_WORKERS is refused with CLLO_E_WORKSPACE (the partials would not
+ *     fit); num_workers == 0 uses min(SM count, CLLO_NOALLOC_MAX_WORKERS).  B, S and the head counts are
+ *     not limited by the scratch: its size depends on the number of workers only.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and remembers it; make that first call outside any stream capture.
+ *   - All calls on one device share the one array and it keeps the previous call's contents.  Nothing
+ *     in it has to start at zero (every partial the merge pass reads was written earlier in the same
+ *     call), but two calls that overlap on the GPU (different streams) race on it: serialise them.
+ */
+#define CLLO_NOALLOC_MAX_WORKERS 160
+int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, float scale, void* o,
+                                 int B, int S, int Hq, int Hkv, int D,
+                                 int kv_layout, int num_workers, void* stream);
+
+/*
  * Log-sum-exp merge of nsplit packed partials:  partials [nsplit][rows][D+2] fp32 -> o [rows][D] bf16.
  * rows = B*Hq.  Splits with l == 0 are ignored.  Same (m, l) monoid as the running update in
  * decode_flash_gqa_kernel.cu:353-371 and TileMaxSumReduce (src/cplusplus/Softmax/softmax_kernel.cu:21-34).
