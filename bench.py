@@ -32,8 +32,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on the headline
-# workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"decode_b60": None, "prefill_nc": None}
+# workload, from the ncu captures summarised under profiles/ (decode: 5 x the B=12 capture, traffic grows
+# with the K/V bytes; prefill: the capture of the workload itself).
+NCU_TRAFFIC_BYTES = {"decode_b60": 5 * 206_274_048, "prefill_nc": 19_081_728}
 
 
 def measured_peaks():
@@ -220,34 +221,32 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
-    # per-step device times on the launching stream (torch's current stream is what the C ABI receives)
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    flush_only = None
+    # device time on the launching stream (torch's current stream is the one the C ABI receives)
     barrier()
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
     if wl == "prefill_nc":
+        # the L2 flush sits between iterations, so each step gets its own pair of events
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         for i in range(args.steps):
             flush.zero_()
             starts[i].record()
             inner()
             ends[i].record()
+        barrier()
+        per_step = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        total_ms = sum(per_step)
     else:
+        t0.record()
         for i in range(args.steps):
-            starts[i].record()
             step_fn()
-            ends[i].record()
-    t1.record()
-    barrier()
-    t_end = time.time()
-    per_step = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-    if wl == "prefill_nc":
-        total_ms = sum(per_step)  # the flush writes sit between the per-step brackets
-    else:
+        t1.record()
+        barrier()
         total_ms = t0.elapsed_time(t1)
+        per_step = [total_ms / args.steps]
+    t_end = time.time()
     # keep the GPU busy with the same kernel a little longer so that the clock samples see load
     if rank == 0 and (t_end - t_begin) < 0.6 and not args.profile:
         reps = int(min(20000, 0.6 / max(total_ms / args.steps / 1e3, 1e-6)))
@@ -316,8 +315,8 @@ def run_ours(args, rank, world, local_rank):
     traffic = NCU_TRAFFIC_BYTES.get(wl)
     roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
-                "kernel": "decode_splitkv_kernel (+decode_merge_kernel in the same bracket)" if bound == "hbm"
-                          else "prefill_fwd_kernel",
+                "kernel": "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
+                          "which also holds the merge pass and launch gaps" if bound == "hbm" else "prefill_fwd_kernel",
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
