@@ -247,20 +247,21 @@ def run_ours(args, rank, world, local_rank):
         total_ms = t0.elapsed_time(t1)
         per_step = [total_ms / args.steps]
     t_end = time.time()
-    # keep the GPU busy with the same kernel a little longer so that the clock samples see load
-    if rank == 0 and (t_end - t_begin) < 0.6 and not args.profile:
-        reps = int(min(20000, 0.6 / max(total_ms / args.steps / 1e3, 1e-6)))
-        for _ in range(reps):
-            step_fn()
-        torch.cuda.synchronize()
-        t_end = time.time()
-        extra["clock_sampling"] = "timed region + %d untimed repeats of the same step" % reps
-    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
-
     tt = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     total_ms = float(tt.item())
+    # keep the GPUs busy with the same step a little longer so that the clock samples see load.  Every rank
+    # runs the same number of repeats (the step may contain a collective), derived from the reduced time.
+    if total_ms < 600.0 and not args.profile:
+        reps = int(min(20000, 600.0 / max(total_ms / args.steps, 1e-3)))
+        for _ in range(reps):
+            step_fn()
+        barrier()
+        t_end = time.time()
+        extra["clock_sampling"] = "timed region + %d untimed repeats of the same step" % reps
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+
     ms_per_step = total_ms / args.steps
     value = total_units / (ms_per_step * 1e-3) / scale_div
 
@@ -339,10 +340,18 @@ def run_ours(args, rank, world, local_rank):
 # ------------------------------------------------------------------------------------------------
 # CPU arms (upstream's own CPU implementation of the decode path)
 # ------------------------------------------------------------------------------------------------
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def _run_ref_binary():
     """One run of the unmodified upstream benchmark program (stubbed runtime): its CPU loop at the headline shape."""
     import oracle_lib as ol
-    out = subprocess.run([ol.REF_BIN], capture_output=True, text=True, timeout=1200)
+    env = dict(os.environ, OMP_NUM_THREADS=str(host_threads()))  # torchrun exports OMP_NUM_THREADS=1
+    out = subprocess.run([ol.REF_BIN], capture_output=True, text=True, timeout=1200, env=env)
     m = re.search(r"CPU time = ([0-9.eE+-]+)s", out.stdout)
     if out.returncode != 0 or not m:
         raise RuntimeError("reference binary failed: " + out.stdout[-400:] + out.stderr[-400:])
@@ -364,7 +373,7 @@ def _port_sample_seconds(B):
 
 def cpu_baseline_decode():
     import oracle_lib as ol
-    cores = ol.lib().cllo_oracle_num_threads()
+    cores = host_threads() if os.path.exists(ol.REF_BIN) else ol.lib().cllo_oracle_num_threads()
     full = decode_bytes(60, 4096, 128, 8)
     if os.path.exists(ol.REF_BIN):
         secs, err = _run_ref_binary()
@@ -382,9 +391,10 @@ def run_reference(args, rank, world):
     """Upstream's CPU implementation on the host cores; rank 0 only."""
     if rank != 0:
         return
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())  # before the OpenMP runtime of the port starts
     import oracle_lib as ol
     ol.build_oracle()
-    cores = ol.lib().cllo_oracle_num_threads()
+    cores = host_threads() if os.path.exists(ol.REF_BIN) else ol.lib().cllo_oracle_num_threads()
     full = decode_bytes(60, 4096, 128, 8)
     if os.path.exists(ol.REF_BIN):
         n = max(1, min(args.steps, 4))  # each run regenerates 1 GB of inputs (~20-30 s); keep the arm to minutes

@@ -21,6 +21,8 @@
 #include "common.cuh"
 #include "host_util.cuh"
 
+#include <cstdlib>
+
 namespace cllo {
 namespace prefill {
 
@@ -41,6 +43,7 @@ constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kDefaultEmu8 = 2;
 
 enum : int {
     SITE_Q_FULL = SITE_PREFILL_BASE + 0,
@@ -166,6 +169,57 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+
+// ---- packed fp32x2 arithmetic (two floats per 64-bit register pair, one instruction) ------------
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^y for a pair, on the special-function unit
+__device__ __forceinline__ void exp2_pair_sfu(uint64_t y, float& p0, float& p1) {
+    float a, b;
+    upk2(y, a, b);
+    p0 = fast_exp2(a);
+    p1 = fast_exp2(b);
+}
+// 2^y for a pair, on the FMA pipes: y = i + f with i = round(y), f in [-0.5, 0.5]; 2^f by a cubic
+// (max relative error 7.5e-5, far below the bf16 rounding of P); 2^i by adding i to the exponent field.
+// The special-function unit delivers 16 results per clock per SM, which for this kernel is as scarce as
+// the tensor pipe, so a fixed share of the exponentials is computed this way.
+__device__ __forceinline__ void exp2_pair_fma(uint64_t y, float& p0, float& p1) {
+    float a, b;
+    upk2(y, a, b);
+    a = fmaxf(a, -126.f);  // also turns -inf (masked) into a denormal-sized result
+    b = fmaxf(b, -126.f);
+    const uint64_t yy = pk2(a, b);
+    const uint64_t t = add2(yy, pk2(12582912.f, 12582912.f));  // 1.5 * 2^23: integer part lands in the low mantissa bits
+    const uint64_t r = add2(t, pk2(-12582912.f, -12582912.f));
+    const uint64_t f = fma2(r, pk2(-1.f, -1.f), yy);
+    uint64_t q = fma2(f, pk2(0.0551716648f, 0.0551716648f), pk2(0.2426111251f, 0.2426111251f));
+    q = fma2(q, f, pk2(0.6932609677f, 0.6932609677f));
+    q = fma2(q, f, pk2(0.9999280572f, 0.9999280572f));
+    float q0, q1, t0, t1;
+    upk2(q, q0, q1);
+    upk2(t, t0, t1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes.
 //   bits [0,14) start >> 4 | [16,30) leading-dim offset >> 4 | [32,46) stride-dim offset >> 4
 //   bits [46,48) = 1 (descriptor version of this architecture) | [61,64) = 2 (128-byte swizzle)
@@ -178,6 +232,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 
+// kEmu8: of every 8 pairs of exponentials, this many are computed on the FMA pipes instead of the
+// special-function unit.
+template <int kEmu8>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -363,28 +420,32 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             float x[128];
             tmem_ld128_wait(s_addr, x);
 
-            // scale into log2 units, mask, row maximum
-            int limit = p.Skv - 1 - j * kBN;  // last valid column of this tile
-            if (p.causal) {
-                const int cl = qi - j * kBN;
-                limit = cl < limit ? cl : limit;
-            }
+            // mask (diagonal / tail tiles only), then the row extreme of the RAW scores: the scale is folded
+            // into the exponent argument below, y = s * c - m with m kept in scaled log2 units
+            const bool neg = p.scale_log2 < 0.f;
             const bool need_mask = (j * kBN + kBN > p.Skv) || (p.causal && (j * kBN + kBN - 1 > q0 + t * kBM));
-            float mx = -INFINITY;
             if (need_mask) {
-#pragma unroll
-                for (int c = 0; c < 128; ++c) {
-                    const float val = (c <= limit) ? x[c] * p.scale_log2 : -INFINITY;
-                    x[c] = val;
-                    mx = fmaxf(mx, val);
+                int limit = p.Skv - 1 - j * kBN;  // last valid column of this tile
+                if (p.causal) {
+                    const int cl = qi - j * kBN;
+                    limit = cl < limit ? cl : limit;
                 }
-            } else {
+                const float masked = neg ? INFINITY : -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 128; ++c) {
-                    x[c] *= p.scale_log2;
-                    mx = fmaxf(mx, x[c]);
-                }
+                for (int c = 0; c < 128; ++c)
+                    if (c > limit) x[c] = masked;
             }
+            float e0 = neg ? INFINITY : -INFINITY, e1 = e0, e2 = e0, e3 = e0;
+#pragma unroll
+            for (int c = 0; c < 128; c += 4) {
+                e0 = neg ? fminf(e0, x[c]) : fmaxf(e0, x[c]);
+                e1 = neg ? fminf(e1, x[c + 1]) : fmaxf(e1, x[c + 1]);
+                e2 = neg ? fminf(e2, x[c + 2]) : fmaxf(e2, x[c + 2]);
+                e3 = neg ? fminf(e3, x[c + 3]) : fmaxf(e3, x[c + 3]);
+            }
+            e0 = neg ? fminf(e0, e1) : fmaxf(e0, e1);
+            e2 = neg ? fminf(e2, e3) : fmaxf(e2, e3);
+            const float mx = (neg ? fminf(e0, e2) : fmaxf(e0, e2)) * p.scale_log2;
 
             // raise the running maximum only when it pays (always on the first tile)
             float alpha = 1.f;
@@ -410,21 +471,28 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
 
             // probabilities (bf16) into tensor memory over the S columns; row sum from the fp32 values
-            float sum = 0.f;
+            const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m, -m);
+            uint64_t sum2 = pk2(0.f, 0.f);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t pk[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const int col = c * 64 + e * 2;
-                    const float p0 = fast_exp2(x[col] - m);
-                    const float p1 = fast_exp2(x[col + 1] - m);
-                    sum += p0 + p1;
+                    const uint64_t y = fma2(pk2(x[col], x[col + 1]), c2, nm2);
+                    float p0, p1;
+                    if ((e * kEmu8) % 8 < kEmu8)
+                        exp2_pair_fma(y, p0, p1);
+                    else
+                        exp2_pair_sfu(y, p0, p1);
+                    sum2 = add2(sum2, pk2(p0, p1));
                     pk[e] = pack_bf16x2(p0, p1);
                 }
                 tmem_st32(s_addr + c * 32, pk);
             }
-            l = l * alpha + sum;
+            float s_lo, s_hi;
+            upk2(sum2, s_lo, s_hi);
+            l = l * alpha + (s_lo + s_hi);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_p_full(t));
@@ -509,12 +577,26 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     if ((rc = encode_bhsd_map(&tm_k, k, B, Hkv, Skv)) != CLLO_OK) return rc;
     if ((rc = encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
 
+    // share of exponentials moved to the FMA pipes, in eighths (tuning knob; default chosen by measurement)
+    static const int emu8 = [] {
+        const char* e = std::getenv("CLLO_PREFILL_EMU8");
+        const int v = e ? std::atoi(e) : kDefaultEmu8;
+        return (v == 0 || v == 2 || v == 3 || v == 4) ? v : kDefaultEmu8;
+    }();
     if (!di->prefill_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         di->prefill_attr_set = true;
     }
-    prefill_fwd_kernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+    const unsigned grid = static_cast<unsigned>(blocks);
+    switch (emu8) {
+        case 0: prefill_fwd_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
+        case 2: prefill_fwd_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
+        case 3: prefill_fwd_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
+        default: prefill_fwd_kernel<4><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
+    }
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }

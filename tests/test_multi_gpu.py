@@ -1,0 +1,64 @@
+"""Two-GPU run of the KV-position-sharded decode over NCCL (skipped on a single-GPU machine)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+pytestmark = pytest.mark.gpu
+SCALE = float(1.0 / np.sqrt(128.0))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    import oracle_lib as ol
+    import cuda_llm_ops_b200 as ops
+    from gpu_util import to_bits, to_dev
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        B, S, Hq, Hkv = 1, 5000, 64, 8
+        q = ol.randn_bf16((B, Hq, 128), 301)
+        k = ol.randn_bf16((B, S, Hkv, 128), 302, std=0.5)
+        v = ol.randn_bf16((B, S, Hkv, 128), 303, std=0.5)
+        s0, s1 = ops.shard_kv_positions(S, world, rank)
+        dec = ops.KVShardedDecoder()
+        out = dec.decode(to_dev(q), to_dev(np.ascontiguousarray(k[:, s0:s1])), to_dev(np.ascontiguousarray(v[:, s0:s1])),
+                         kv_layout=ops.KV_BSHD)
+        torch.cuda.synchronize()
+        single = ops.gqa_decode(to_dev(q), to_dev(k), to_dev(v), kv_layout=ops.KV_BSHD)
+        torch.cuda.synchronize()
+        want = ol.decode(q, k, v, SCALE, 0)
+        res = list(ol.errors(to_bits(out), want)) + list(ol.errors(to_bits(out), to_bits(single)))
+        rc, _ = ops.device_status()
+        np.save(os.path.join(out_dir, "r%d.npy" % rank), np.array(res + [float(rc)]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_position_sharded_decode_matches_oracle_and_single_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        mx, mean, rel, mx1, mean1, rel1, rc = np.load(os.path.join(str(tmp_path), "r%d.npy" % r))
+        assert rc == 0
+        assert mx <= 2e-2 and mean <= 2e-3 and rel <= 2e-2, (r, mx, mean, rel)          # vs CPU oracle
+        assert mx1 <= 4e-3 and rel1 <= 5e-3, (r, mx1, mean1, rel1)                       # vs the 1-GPU result
