@@ -43,7 +43,7 @@ constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kDefaultEmu8 = 2;
+constexpr int kDefaultEmu8 = 0;
 
 enum : int {
     SITE_Q_FULL = SITE_PREFILL_BASE + 0,
