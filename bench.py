@@ -155,13 +155,13 @@ def run_ours(args, rank, world, local_rank):
                   "l2": "inputs (%.2f GB per GPU) exceed the 126 MB L2; no flush needed" % (units_per_rank / 1e9)}
         host_in = [q, k, v]
     elif wl == "decode_long":
-        S_total, Hq, Hkv = 1 << 20, 64, 8
+        S_total, Hq, Hkv = (args.kv_len or (1 << 20)), 64, 8
         s0, s1 = ops.shard_kv_positions(S_total, world, rank)
         q = randn_bf16((1, Hq, 128), 0.5)
         if world > 1:
             dist.broadcast(q, 0)
         k, v = randn_bf16((1, s1 - s0, Hkv, 128), 0.5), randn_bf16((1, s1 - s0, Hkv, 128), 0.5)
-        dec = ops.KVShardedDecoder() if world > 1 else None
+        dec = ops.KVShardedDecoder(exchange=args.exchange) if world > 1 else None
         part = torch.zeros((1, 1, Hq, 130), dtype=torch.float32, device=dev)
         if world > 1:
             step_fn = lambda: dec.decode(q, k, v, kv_layout=ops.KV_BSHD)  # noqa: E731
@@ -174,7 +174,7 @@ def run_ours(args, rank, world, local_rank):
         units_per_rank = decode_bytes(1, s1 - s0, Hq, Hkv)
         metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
         scaling = "strong"
-        config = {"workload": "decode_long: one sequence, S=1048576, Hq=64, Hkv=8, D=128, K/V [1,S,Hkv,D] 0.5*N(0,1)",
+        config = {"workload": "decode_long: one sequence, S=%d, Hq=64, Hkv=8, D=128, K/V [1,S,Hkv,D] 0.5*N(0,1)" % S_total,
                   "global_batch": 1, "kv_seq_len": S_total,
                   "sharding": "KV positions; all-gather of (O,m,l) partials + LSE combine" if world > 1 else "none",
                   "l2": "inputs exceed L2"}
@@ -307,6 +307,9 @@ def run_ours(args, rank, world, local_rank):
     rc, detail = ops.device_status()
     if rc != 0:
         raise SystemExit("device status %d %s" % (rc, detail))
+    if wl == "decode_long" and world > 1:
+        config["exchange"] = dec.exchange
+        launches_per_step = 3 if dec.exchange == "peer" else 4  # decode, merge, exchange+combine | all-gather, combine
 
     if rank != 0:
         return
@@ -432,6 +435,10 @@ def main():
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="decode_long on several GPUs: how the per-GPU partials are exchanged")
+    ap.add_argument("--kv-len", type=int, default=0,
+                    help="decode_long only: override the total KV length (profiling one GPU's share of a sharded run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="for runs under a profiler: no CPU baseline, no end-to-end leg, no clock-sampling repeats")

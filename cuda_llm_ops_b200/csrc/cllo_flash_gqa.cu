@@ -2,6 +2,7 @@
 // share one device status word.
 #include "gqa_decode.cuh"
 #include "gqa_prefill.cuh"
+#include "gqa_exchange.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -141,8 +142,6 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
         // launched with programmatic stream serialization: its blocks become resident while the main
         // kernel drains and start the moment that grid has completed
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(plan.units));
-        cfg.blockDim = dim3(decode::kMergeThreads);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
@@ -150,7 +149,15 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel, p));
+        if (plan.many_pieces) {
+            cfg.gridDim = dim3(static_cast<unsigned>(plan.units * decode::kRows));
+            cfg.blockDim = dim3(8 * 32);
+            CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel<8, 1>, p));
+        } else {
+            cfg.gridDim = dim3(static_cast<unsigned>(plan.units));
+            cfg.blockDim = dim3(decode::kRows * 32);
+            CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel<1, decode::kRows>, p));
+        }
     }
     return CLLO_OK;
 }
@@ -163,6 +170,12 @@ int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long 
         partials, nsplit, rows, static_cast<__nv_bfloat16*>(o));
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
+}
+
+int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer_gather, void* const* peer_flags,
+                                   int rank, int world, unsigned epoch, void* o, long long rows, int D, void* stream) {
+    return exchange::launch(local_partial, peer_gather, peer_flags, rank, world, epoch, o, rows, D,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,

@@ -21,6 +21,7 @@ enum : int {
     SITE_DECODE_EMPTY = 2,
     SITE_DECODE_DRAIN = 3,
     SITE_DECODE_ISSUE = 4,
+    SITE_EXCHANGE_FLAG = 8,
     SITE_PREFILL_BASE = 16,
 };
 

@@ -387,10 +387,16 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
 }
 
-// Second pass over the units that a worker boundary cut.  grid = units, block = 512: thread (row, 4 dims).
-constexpr int kMergeThreads = kRows * (kD / 4);
-__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Params p) {
-    const long long u = blockIdx.x;
+// Second pass over the units that a worker boundary cut.  A block covers RB query-head rows of one unit
+// with PL piece-lanes x RB rows x 32 dim-lanes (4 dims each) threads.  Two shapes are used:
+//   <1,16>: many units cut in two or three pieces (a batch of sequences): one block per unit, no
+//           shared-memory step;
+//   <8,1> : few units cut into many pieces (one long sequence spread over all SMs): one block per row,
+//           pieces merged eight at a time, so the cost is a few load latencies instead of one per piece.
+template <int PL, int RB>
+__global__ void __launch_bounds__(PL * RB * 32) decode_merge_kernel(const Params p) {
+    constexpr int kBlocksPerUnit = kRows / RB;
+    const long long u = blockIdx.x / kBlocksPerUnit;
     const long long t_first = u * p.n_t, t_last = t_first + p.n_t - 1;
     const long long w_lo = worker_of_tile(t_first, p.T, p.W), w_hi = worker_of_tile(t_last, p.T, p.W);
     if (w_lo == w_hi) return;  // the unit lived inside one worker, which wrote the final result
@@ -398,10 +404,16 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Param
     const int kvh = static_cast<int>((u / p.n_gblk) % p.Hkv);
     const int b = static_cast<int>(u / (static_cast<long long>(p.n_gblk) * p.Hkv));
     const int rows = (p.G - gblk * kRows) < kRows ? (p.G - gblk * kRows) : kRows;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c4 = lane * 4;
+    const int pg = warp / RB;
+    const int r = static_cast<int>(blockIdx.x % kBlocksPerUnit) * RB + warp % RB;
+    if (r >= rows) return;  // with PL > 1 a block holds one row, so this exit is taken by whole blocks
     const long long head0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * p.G + gblk * kRows;
     const int which_lo = (worker_lo(w_lo, p.T, p.W) == t_first) ? 0 : 1;
-    const int r = threadIdx.x >> 5, c4 = (threadIdx.x & 31) * 4;
-    if (r >= rows) return;
+    __shared__ float s_max[PL];
+    __shared__ float s_l[PL];
+    __shared__ float4 s_acc[PL][32];
+    static_assert(PL == 1 || RB == 1, "the shared-memory reduction assumes one row per block");
     pdl_wait_prior_grid();
     auto row_ptr = [&](long long w) {
         return p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
@@ -409,24 +421,46 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Param
     // branch-free bodies so that the loads of several pieces are in flight together
     float mstar = -INFINITY;
 #pragma unroll 4
-    for (long long w = w_lo; w <= w_hi; ++w) {
+    for (long long w = w_lo + pg; w <= w_hi; w += PL) {
         const float2 ml = *reinterpret_cast<const float2*>(row_ptr(w) + kD);
         mstar = fmaxf(mstar, ml.y > 0.f ? ml.x : -INFINITY);
     }
+    if constexpr (PL > 1) {
+        if (lane == 0) s_max[pg] = mstar;
+        __syncthreads();
+        mstar = s_max[0];
+#pragma unroll
+        for (int i = 1; i < PL; ++i) mstar = fmaxf(mstar, s_max[i]);
+    }
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
 #pragma unroll 4
-    for (long long w = w_lo; w <= w_hi; ++w) {
+    for (long long w = w_lo + pg; w <= w_hi; w += PL) {
         const float* row = row_ptr(w);
         const float2 ml = *reinterpret_cast<const float2*>(row + kD);
-        const float l = ml.y;
-        const float wgt = l > 0.f ? __expf(ml.x - mstar) : 0.f;
+        const float wgt = ml.y > 0.f ? __expf(ml.x - mstar) : 0.f;
         const float2 x = *reinterpret_cast<const float2*>(row + c4);
         const float2 y = *reinterpret_cast<const float2*>(row + c4 + 2);
         a0 += wgt * x.x;
         a1 += wgt * x.y;
         a2 += wgt * y.x;
         a3 += wgt * y.y;
-        lsum += wgt * l;
+        lsum += wgt * ml.y;
+    }
+    if constexpr (PL > 1) {
+        s_acc[pg][lane] = make_float4(a0, a1, a2, a3);
+        if (lane == 0) s_l[pg] = lsum;
+        __syncthreads();
+        if (pg != 0) return;
+        lsum = s_l[0];
+#pragma unroll
+        for (int i = 1; i < PL; ++i) {  // fixed order: deterministic
+            const float4 t = s_acc[i][lane];
+            a0 += t.x;
+            a1 += t.y;
+            a2 += t.z;
+            a3 += t.w;
+            lsum += s_l[i];
+        }
     }
     if (p.partial_out) {
         float* dst = p.partial_out + (head0 + r) * kPW;
@@ -473,6 +507,7 @@ struct Plan {
     Params prm;
     size_t ws_bytes;
     bool needs_merge;
+    bool many_pieces;  // some unit is cut into more than four pieces
     long long units;
 };
 
@@ -489,6 +524,7 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     p.n_gblk = (p.G + kRows - 1) / kRows;
     p.n_t = (S + kTok - 1) / kTok;
     plan->units = static_cast<long long>(B) * Hkv * p.n_gblk;
+    if (plan->units * kRows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // grid of the merge pass
     p.T = plan->units * p.n_t;
     long long W = num_workers > 0 ? num_workers : sm_count;
     if (W > p.T) W = p.T;
@@ -496,6 +532,7 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     p.W = static_cast<int>(W);
     if (p.T / W + 1 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // a worker's tile count is a 32-bit loop index
     plan->ws_bytes = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
+    plan->many_pieces = (p.n_t / (p.T / W > 0 ? p.T / W : 1)) + 2 > 4;
     plan->needs_merge = false;
     for (long long w = 1; w < W; ++w)
         if (worker_lo(w, p.T, W) % p.n_t != 0) {

@@ -121,6 +121,25 @@ int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, fl
 int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long rows, int D, void* stream);
 
 /*
+ * Exchange + merge for one sequence whose KV cache is sharded by position over the GPUs of one node:
+ * all-gather of every rank's packed partial and the log-sum-exp combine, in one kernel over peer memory
+ * (plain peer stores and flag words; no library collective).  Upstream has no multi-GPU code; this
+ * replaces "ncclAllGather + cllo_gqa_combine_bf16" when the ranks can map each other's memory.
+ *
+ *   local_partial [rows][D+2]: this rank's partial (the partial_out of cllo_gqa_decode_bf16).
+ *   peer_gather, peer_flags: HOST arrays of `world` device pointers, entry p = rank p's gather buffer
+ *       ([2][world][rows][D+2] fp32) and flag words ([world] uint32, zeroed once before the first call),
+ *       as mapped into THIS process (e.g. CUDA IPC / symmetric memory); entry `rank` is the local one.
+ *   epoch: 1, 2, 3, ... the same on every rank for the same step.  Every rank must make the call; a
+ *       rank that never does makes the others' bounded wait (about a second) expire, which is reported
+ *       through cllo_device_status() with results left invalid.
+ *   o [rows][D] bf16: the merged output, produced on every rank.
+ */
+#define CLLO_MAX_PEERS 16
+int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer_gather, void* const* peer_flags,
+                                   int rank, int world, unsigned epoch, void* o, long long rows, int D, void* stream);
+
+/*
  * Multi-token (prefill) GQA forward:  O = softmax(mask(scale * Q K^T)) V,  lse = m + log(l).
  * Stands in for flash_gqa_forward_bf16_kernel + launch_flash_gqa_forward_bf16_kernel
  * (src/python/Triton/flash_gqa_kernel.py:16-138, :185-338).  Layout as upstream:

@@ -44,6 +44,14 @@ def test_argument_validation_needs_no_gpu(built_library):
     assert lib.cllo_gqa_combine_bf16(None, 1, None, 1, 128, None) == _lib.E_BAD_ARG
     assert lib.cllo_gqa_prefill_fwd_bf16(None, None, None, 1.0, 0, None, None, 1, 1, 1, 1, 1, 128, None) == _lib.E_BAD_ARG
     assert lib.cllo_status_string(_lib.E_WORKSPACE).decode().startswith("workspace")
+    # peer exchange: null tables, rank outside the world, epoch 0, too many peers
+    two = (ctypes.c_void_p * 2)(1 << 20, 2 << 20)
+    ex = lib.cllo_gqa_exchange_combine_bf16
+    assert ex(None, None, None, 0, 2, 1, None, 64, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 2, 2, 1, 1 << 20, 64, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 0, 2, 0, 1 << 20, 64, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 0, 17, 1, 1 << 20, 64, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 0, 2, 1, 1 << 20, 64, 64, None) == _lib.E_UNSUPPORTED
 
 
 def test_decode_plan_balances_tiles(built_library):

@@ -36,16 +36,25 @@ def _worker(rank, world, port, out_dir):
         k = ol.randn_bf16((B, S, Hkv, 128), 302, std=0.5)
         v = ol.randn_bf16((B, S, Hkv, 128), 303, std=0.5)
         s0, s1 = ops.shard_kv_positions(S, world, rank)
-        dec = ops.KVShardedDecoder()
-        out = dec.decode(to_dev(q), to_dev(np.ascontiguousarray(k[:, s0:s1])), to_dev(np.ascontiguousarray(v[:, s0:s1])),
-                         kv_layout=ops.KV_BSHD)
+        qd, kd, vd = to_dev(q), to_dev(np.ascontiguousarray(k[:, s0:s1])), to_dev(np.ascontiguousarray(v[:, s0:s1]))
+        dec = ops.KVShardedDecoder(exchange="nccl")
+        out = dec.decode(qd, kd, vd, kv_layout=ops.KV_BSHD)
         torch.cuda.synchronize()
+        # the one-kernel exchange over peer memory must give the same answer, call after call (gather slots
+        # alternate by call parity, flag words carry a growing epoch)
+        peer = ops.KVShardedDecoder(exchange="auto")
+        peer_err = 0.0
+        for _ in range(5):
+            out_p = peer.decode(qd, kd, vd, kv_layout=ops.KV_BSHD)
+            torch.cuda.synchronize()
+            peer_err = max(peer_err, ol.errors(to_bits(out_p), to_bits(out))[0])
+        used_peer = 1.0 if peer.exchange == "peer" else 0.0
         single = ops.gqa_decode(to_dev(q), to_dev(k), to_dev(v), kv_layout=ops.KV_BSHD)
         torch.cuda.synchronize()
         want = ol.decode(q, k, v, SCALE, 0)
         res = list(ol.errors(to_bits(out), want)) + list(ol.errors(to_bits(out), to_bits(single)))
         rc, _ = ops.device_status()
-        np.save(os.path.join(out_dir, "r%d.npy" % rank), np.array(res + [float(rc)]))
+        np.save(os.path.join(out_dir, "r%d.npy" % rank), np.array(res + [float(rc), peer_err, used_peer]))
     finally:
         dist.destroy_process_group()
 
@@ -58,7 +67,9 @@ def test_two_gpu_position_sharded_decode_matches_oracle_and_single_gpu(tmp_path)
     port = _free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
-        mx, mean, rel, mx1, mean1, rel1, rc = np.load(os.path.join(str(tmp_path), "r%d.npy" % r))
+        mx, mean, rel, mx1, mean1, rel1, rc, peer_err, used_peer = np.load(os.path.join(str(tmp_path), "r%d.npy" % r))
         assert rc == 0
+        assert peer_err <= 1e-6, peer_err  # same partials, same merge order: identical to the NCCL path
+        print("rank %d peer exchange in use: %s" % (r, bool(used_peer)))
         assert mx <= 2e-2 and mean <= 2e-3 and rel <= 2e-2, (r, mx, mean, rel)          # vs CPU oracle
         assert mx1 <= 4e-3 and rel1 <= 5e-3, (r, mx1, mean1, rel1)                       # vs the 1-GPU result
