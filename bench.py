@@ -164,7 +164,8 @@ def run_ours(args, rank, world, local_rank):
         dec = ops.KVShardedDecoder(exchange=args.exchange) if world > 1 else None
         part = torch.zeros((1, 1, Hq, 130), dtype=torch.float32, device=dev)
         if world > 1:
-            step_fn = lambda: dec.decode(q, k, v, kv_layout=ops.KV_BSHD)  # noqa: E731
+            out = torch.empty_like(q)
+            step_fn = lambda: dec.decode(q, k, v, kv_layout=ops.KV_BSHD, out=out)  # noqa: E731
             launches_per_step = 3
         else:
             out = torch.empty_like(q)
@@ -216,6 +217,21 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         step_fn()
     barrier()
+    if wl == "decode_long" and world > 1 and dec.exchange == "peer" and not args.no_graph:
+        # the three kernels of a step (decode, merge, exchange+combine) replayed from a CUDA graph: at ~100 us
+        # per step on 8 GPUs, host launch jitter between the ranks otherwise shows up as waiting in the exchange
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                step_fn()
+        torch.cuda.current_stream().wait_stream(side)
+        step_fn = graph.replay
+        config["launch"] = "CUDA graph replay"
+        for _ in range(3):
+            step_fn()
+        barrier()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -439,6 +455,7 @@ def main():
                     help="decode_long on several GPUs: how the per-GPU partials are exchanged")
     ap.add_argument("--kv-len", type=int, default=0,
                     help="decode_long only: override the total KV length (profiling one GPU's share of a sharded run)")
+    ap.add_argument("--no-graph", action="store_true", help="decode_long on several GPUs: launch eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="for runs under a profiler: no CPU baseline, no end-to-end leg, no clock-sampling repeats")

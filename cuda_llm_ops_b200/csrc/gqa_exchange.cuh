@@ -47,8 +47,15 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads) exchange_combine_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads) exchange_combine_kernel(Params p) {
     const int dst = blockIdx.x;  // destination rank served by this block; also its share of the rows in step 3
+    // epoch 0 = "count the calls on the device": every launch has exactly `world` blocks, each takes one
+    // ticket, so all blocks of the n-th launch derive n.  This keeps the call replayable from a CUDA graph.
+    __shared__ unsigned s_epoch;
+    if (threadIdx.x == 0)
+        s_epoch = p.epoch ? p.epoch : atomicAdd(p.flags[p.rank] + p.world, 1u) / static_cast<unsigned>(p.world) + 1u;
+    __syncthreads();
+    p.epoch = s_epoch;
     const size_t slot_floats = static_cast<size_t>(p.rows) * kPW;
     const size_t parity_off = static_cast<size_t>(p.epoch & 1u) * p.world * slot_floats;
 
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(kThreads) exchange_combine_kernel(const Params
 static int launch(const float* local, void* const* gather, void* const* flags, int rank, int world, unsigned epoch,
                   void* o, long long rows, int D, cudaStream_t stream) {
     if (!local || !gather || !flags || !o || rows <= 0) return CLLO_E_BAD_ARG;
-    if (world < 1 || world > CLLO_MAX_PEERS || rank < 0 || rank >= world || epoch == 0) return CLLO_E_BAD_ARG;
+    if (world < 1 || world > CLLO_MAX_PEERS || rank < 0 || rank >= world) return CLLO_E_BAD_ARG;
     if (D != kD) return CLLO_E_UNSUPPORTED;
     Params p;
     p.local = local;

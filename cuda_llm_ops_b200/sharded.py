@@ -45,7 +45,8 @@ def shard_kv_positions(seq_len, world_size, rank, align=64):
 class _PeerBuffers:
     """Gather slots and flag words in memory that every rank of the node can address (torch symmetric memory).
 
-    Layout per rank: [2 parities][world][rows][D+2] fp32 gather slots, then `world` uint32 flag words.
+    Layout per rank: [2 parities][world][rows][D+2] fp32 gather slots, then `world` uint32 flag words and
+    one launch counter.
     """
 
     def __init__(self, group, rows, device):
@@ -147,7 +148,11 @@ class KVShardedDecoder:
             # NCCL gathers in place (this rank's slot already holds its partial); CPU backends get a copy
             src = mine.reshape(-1) if mine.is_cuda else mine.reshape(-1).clone()
             dist.all_gather_into_tensor(gathered.view(-1), src, group=self.group)
-        return self._combine(gathered)
+        merged = self._combine(gathered)
+        if out is not None:
+            out.copy_(merged)
+            return out
+        return merged
 
     def _decode_peer(self, q, k_local, v_local, scale, kv_layout, out):
         B, Hq, D = q.shape
@@ -157,10 +162,10 @@ class KVShardedDecoder:
         if out is None:
             out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=q.device)
         peer = self._peer
-        peer.epoch += 1
         with torch.cuda.device(q.device):
+            # epoch 0: the kernel counts its launches on the device, so this call can sit in a CUDA graph
             rc = _lib.load().cllo_gqa_exchange_combine_bf16(
-                self._local.data_ptr(), peer.gather_ptrs, peer.flag_ptrs, self.rank, self.world_size, peer.epoch,
+                self._local.data_ptr(), peer.gather_ptrs, peer.flag_ptrs, self.rank, self.world_size, 0,
                 out.data_ptr(), B * Hq, D, torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "cllo_gqa_exchange_combine_bf16")
         return out

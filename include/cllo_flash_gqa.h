@@ -128,9 +128,11 @@ int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long 
  *
  *   local_partial [rows][D+2]: this rank's partial (the partial_out of cllo_gqa_decode_bf16).
  *   peer_gather, peer_flags: HOST arrays of `world` device pointers, entry p = rank p's gather buffer
- *       ([2][world][rows][D+2] fp32) and flag words ([world] uint32, zeroed once before the first call),
- *       as mapped into THIS process (e.g. CUDA IPC / symmetric memory); entry `rank` is the local one.
- *   epoch: 1, 2, 3, ... the same on every rank for the same step.  Every rank must make the call; a
+ *       ([2][world][rows][D+2] fp32) and flag words ([world + 1] uint32, zeroed once before the first
+ *       call), as mapped into THIS process (e.g. CUDA IPC / symmetric memory); entry `rank` is the local one.
+ *   epoch: 1, 2, 3, ... the same on every rank for the same step; or 0 on every rank and every call, in
+ *       which case the kernel counts its own launches in the extra flag word (a call sequence that never
+ *       changes its arguments, e.g. one replayed from a CUDA graph).  Every rank must make the call; a
  *       rank that never does makes the others' bounded wait (about a second) expire, which is reported
  *       through cllo_device_status() with results left invalid.
  *   o [rows][D] bf16: the merged output, produced on every rank.
