@@ -8,7 +8,8 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
     decode_long     one sequence, S=1,048,576, Hq=64, Hkv=8, KV sharded by position across GPUs
                     (all-gather of per-GPU partials + LSE combine; strong scaling)
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
-    prefill_causal  prefill forward, causal, B=8 per... see --help; batch-sharded
+    prefill_causal  prefill forward, causal, B=8 in total (strong scaling), S=16384, Hq=64, Hkv=8; batch-sharded
+    swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
 
 A step is one pass of the hot path over one batch.  `value` is whole-job throughput with inputs
 resident in HBM; `e2e` is the same metric through the package's public launcher with HOST buffers
@@ -180,6 +181,27 @@ def run_ours(args, rank, world, local_rank):
                   "sharding": "KV positions; all-gather of (O,m,l) partials + LSE combine" if world > 1 else "none",
                   "l2": "inputs exceed L2"}
         host_in = [q, k, v]
+    elif wl == "swa":
+        # upstream's sliding-window benchmark shape (README: 280 us / 61 TFLOPS on an RTX 5080 Laptop)
+        B, S, Hq, Hkv, window = 1, 4096, 16, 1, 512
+        q, k, v = randn_bf16((B, Hq, S, 128)), randn_bf16((B, Hkv, S, 128)), randn_bf16((B, Hkv, S, 128))
+        sink = torch.rand(Hq, device=dev, generator=gen) + 0.5
+        out = torch.empty_like(q)
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.launch_flash_swa_forward_bf16_kernel(q, k, v, out=out, lse=lse, window_size=window,  # noqa: E731
+                                                                 sink_value=sink)
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        # upstream's own FLOP convention: 2 * Sq * window * (Dqk + Dv) per head (test_flash_swa_kernel.py:318-337)
+        units_per_rank = 2.0 * S * window * 256 * B * Hq
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "swa_prefill_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "swa: sliding-window forward with sink, B=1, S=4096, Hq=16, Hkv=1, D=128, window=512",
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [q, k, v]
     elif wl in ("prefill_nc", "prefill_causal"):
         causal = wl == "prefill_causal"
         if causal:
@@ -242,7 +264,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl == "prefill_nc":
+    if wl in ("prefill_nc", "swa"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -447,7 +469,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

@@ -15,6 +15,7 @@ from .flash_gqa import (  # noqa: F401
     gqa_decode,
     launch_decode_flash_gqa_bf16_kernel,
     launch_flash_gqa_forward_bf16_kernel,
+    launch_flash_swa_forward_bf16_kernel,
 )
 from .sharded import (  # noqa: F401
     KVShardedDecoder,

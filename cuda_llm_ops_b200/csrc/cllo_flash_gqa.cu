@@ -180,7 +180,15 @@ int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer
 
 int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
                               float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
-    return prefill::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D,
+    return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int window_size,
+                              const float* sink_value, void* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv,
+                              int D, void* stream) {
+    if (window_size <= 0 || !sink_value) return CLLO_E_BAD_ARG;
+    return prefill::launch(q, k, v, scale, 1, window_size, sink_value, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
 }
 

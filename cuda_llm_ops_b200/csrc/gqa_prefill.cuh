@@ -62,6 +62,8 @@ struct Params {
     float* lse;  // nullable
     float scale_log2;
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qp;
+    int window;         // > 0: sliding window, a query sees kv in [q - (window - 1), q] (implies causal)
+    const float* sink;  // nullable, [Hq]: per-head term added to the softmax denominator
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
@@ -269,12 +271,17 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int h = kvh * p.G + g;
     const int q0 = qp * (kTiles * kBM);
 
-    int n_kv = (p.Skv + kBN - 1) / kBN;
+    // KV tiles [j_lo, j_hi) can hold something visible to this block's rows
+    int j_hi = (p.Skv + kBN - 1) / kBN;
     if (p.causal) {
         const int last_row = q0 + kTiles * kBM - 1;
         const int lim = last_row / kBN + 1;
-        n_kv = lim < n_kv ? lim : n_kv;
+        j_hi = lim < j_hi ? lim : j_hi;
     }
+    int j_lo = 0;
+    if (p.window > 0 && q0 - (p.window - 1) > 0) j_lo = (q0 - (p.window - 1)) / kBN;
+    if (j_lo > j_hi - 1) j_lo = j_hi - 1;
+    const int n_kv = j_hi - j_lo;  // >= 1; the loops below count local tiles, tile j is global tile j_lo + j
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q_full, 1);
@@ -320,13 +327,13 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 mbar_wait(bar_k_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_K_EMPTY, j);
                 mbar_arrive_expect_tx(bar_k_full(s), kTileBytes);
                 const uint32_t kd = base + kSmemK + s * kTileBytes;
-                tma_load_4d(kd, &tm_k, bar_k_full(s), 0, j * kBN, kvh, b);
-                tma_load_4d(kd + kHalfBytes, &tm_k, bar_k_full(s), 64, j * kBN, kvh, b);
+                tma_load_4d(kd, &tm_k, bar_k_full(s), 0, (j_lo + j) * kBN, kvh, b);
+                tma_load_4d(kd + kHalfBytes, &tm_k, bar_k_full(s), 64, (j_lo + j) * kBN, kvh, b);
                 mbar_wait(bar_v_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_V_EMPTY, j);
                 mbar_arrive_expect_tx(bar_v_full(s), kTileBytes);
                 const uint32_t vd = base + kSmemV + s * kTileBytes;
-                tma_load_4d(vd, &tm_v, bar_v_full(s), 0, j * kBN, kvh, b);
-                tma_load_4d(vd + kHalfBytes, &tm_v, bar_v_full(s), 64, j * kBN, kvh, b);
+                tma_load_4d(vd, &tm_v, bar_v_full(s), 0, (j_lo + j) * kBN, kvh, b);
+                tma_load_4d(vd + kHalfBytes, &tm_v, bar_v_full(s), 64, (j_lo + j) * kBN, kvh, b);
             }
             if (*abort_flag) {
                 // a wait gave up somewhere: let the copies already issued land before the block retires
@@ -423,17 +430,20 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             // mask (diagonal / tail tiles only), then the row extreme of the RAW scores: the scale is folded
             // into the exponent argument below, y = s * c - m with m kept in scaled log2 units
             const bool neg = p.scale_log2 < 0.f;
-            const bool need_mask = (j * kBN + kBN > p.Skv) || (p.causal && (j * kBN + kBN - 1 > q0 + t * kBM));
+            const int kv0 = (j_lo + j) * kBN;  // first kv position of this tile
+            const bool need_mask = (kv0 + kBN > p.Skv) || (p.causal && (kv0 + kBN - 1 > q0 + t * kBM)) ||
+                                   (p.window > 0 && (kv0 < q0 + t * kBM + kBM - 1 - (p.window - 1)));
             if (need_mask) {
-                int limit = p.Skv - 1 - j * kBN;  // last valid column of this tile
+                int limit = p.Skv - 1 - kv0;  // last valid column of this tile
                 if (p.causal) {
-                    const int cl = qi - j * kBN;
+                    const int cl = qi - kv0;
                     limit = cl < limit ? cl : limit;
                 }
+                const int first = p.window > 0 ? qi - (p.window - 1) - kv0 : 0;  // first valid column
                 const float masked = neg ? INFINITY : -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 128; ++c)
-                    if (c > limit) x[c] = masked;
+                    if (c > limit || c < first) x[c] = masked;
             }
             float e0 = neg ? INFINITY : -INFINITY, e1 = e0, e2 = e0, e3 = e0;
 #pragma unroll
@@ -453,7 +463,8 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = fmaxf(m, mx);
                 if (j > 0) {
-                    alpha = fast_exp2(m - m_new);
+                    // a lane taken along by the warp vote may still have seen no visible key (sliding window)
+                    alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m - m_new);
                     mbar_wait(bar_o_full(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
                     __syncwarp();
                     tc_fence_after();
@@ -471,7 +482,10 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
 
             // probabilities (bf16) into tensor memory over the S columns; row sum from the fp32 values
-            const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m, -m);
+            // a row that has not seen a visible key yet (sliding window) still has m = -inf: its scores are all
+            // masked, so any finite reference gives the right probabilities (zeros)
+            const float m_ref = (m == -INFINITY) ? 0.f : m;
+            const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m_ref, -m_ref);
             uint64_t sum2 = pk2(0.f, 0.f);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -502,7 +516,11 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_wait(bar_o_full(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
         __syncwarp();
         tc_fence_after();
-        const float inv_l = 1.f / l;
+        // optional sink term in the denominator; rows without any visible key give zeros
+        const float sink = p.sink ? p.sink[h] : 0.f;
+        const bool visible = l > 0.f;
+        const float denom = l + ((p.sink && visible) ? sink * fast_exp2(-m) : 0.f);
+        const float inv_l = visible ? 1.f / denom : 0.f;
         const bool row_ok = qi < p.Sq;
         __nv_bfloat16* orow = p.o + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + qi) * kD;
 #pragma unroll 1
@@ -522,7 +540,8 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
         }
         if (row_ok && p.lse)
-            p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] = (m + log2f(l)) * kLn2;
+            p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] =
+                visible ? (m + log2f(denom)) * kLn2 : (p.sink ? logf(fmaxf(sink, 1.0e-9f)) : -INFINITY);
         tc_fence_before();
     }
 
@@ -545,8 +564,9 @@ static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, in
     return encode_bf16_4d(map, basep, dims, strides, box);
 }
 
-static int launch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
-                  int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+static int launch(const void* q, const void* k, const void* v, float scale, int causal, int window, const float* sink,
+                  void* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+    if (window < 0) return CLLO_E_BAD_ARG;
     if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
     if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return CLLO_E_BAD_ARG;
     if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
@@ -567,7 +587,9 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     p.Hq = Hq;
     p.Hkv = Hkv;
     p.G = Hq / Hkv;
-    p.causal = causal ? 1 : 0;
+    p.causal = (causal || window > 0) ? 1 : 0;
+    p.window = window;
+    p.sink = sink;
     p.n_qp = (Sq + kTiles * kBM - 1) / (kTiles * kBM);
     const long long blocks = static_cast<long long>(B) * Hq * p.n_qp;
     if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;

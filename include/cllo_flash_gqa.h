@@ -152,6 +152,18 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               void* o, float* lse,
                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
+/*
+ * Sliding-window attention forward with a sink term (the mask variant of the prefill forward):
+ * a query at position i sees kv positions [i - (window_size - 1), i]; the softmax denominator of head h
+ * is sum(exp(s - m)) + sink_value[h] * exp(-m); rows without any visible key give zeros and
+ * lse = log(max(sink, 1e-9)).  Stands in for flash_swa_forward_bf16_kernel +
+ * launch_flash_swa_forward_bf16_kernel (src/python/Triton/SWA/flash_swa_kernel.py:15-160, :186-330).
+ * Same tensors and layouts as cllo_gqa_prefill_fwd_bf16; sink_value is fp32 [Hq] on the device.
+ */
+int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int window_size,
+                              const float* sink_value, void* o, float* lse,
+                              int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -276,3 +276,81 @@ int cllo_oracle_gqa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uin
     }
     return failed ? -2 : 0;
 }
+
+/*
+ * Sliding-window attention forward with a sink term, layout as the prefill oracle above.
+ *
+ * Follows examples/python/Triton/test_flash_swa_kernel.py:28-118: a query at position i sees kv in
+ * [i - (window - 1), i] (:84-86); fp32 scores * scale masked to -inf (:93-94); row max (:95);
+ * denom = sum exp(s - max) + sink[h] * exp(-max) (:96-98); probs = exp / denom (:99);
+ * lse = log(denom) + max (:100); out = probs @ V rounded to bf16 (:101-107).  A row that sees no key at all
+ * (possible when Sq > Skv) is defined as in the upstream kernel (src/python/Triton/SWA/flash_swa_kernel.py:
+ * has_visible_kv): zeros and lse = log(max(sink, 1e-9)).
+ */
+int cllo_oracle_swa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, float scale,
+                                 int window, const float* sink, uint16_t* o, float* lse,
+                                 int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || window <= 0 || !sink) return -1;
+    if (Hq % Hkv != 0) return -1;
+    const int G = Hq / Hkv;
+    const int64_t total = (int64_t)B * Hq * Sq;
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* sc = (float*)malloc(sizeof(float) * (size_t)Skv);
+        float* oacc = (float*)malloc(sizeof(float) * (size_t)D);
+        float* qf = (float*)malloc(sizeof(float) * (size_t)D);
+        if (!sc || !oacc || !qf) {
+#pragma omp atomic write
+            failed = 1;
+        } else {
+#pragma omp for schedule(dynamic, 16)
+            for (int64_t idx = 0; idx < total; ++idx) {
+                const int64_t b = idx / ((int64_t)Hq * Sq);
+                const int64_t h = (idx / Sq) % Hq;
+                const int64_t i = idx % Sq;
+                const int64_t kvh = h / G;
+                const uint16_t* qrow = q + ((b * Hq + h) * Sq + i) * D;
+                const uint16_t* kb = k + (b * Hkv + kvh) * (int64_t)Skv * D;
+                const uint16_t* vb = v + (b * Hkv + kvh) * (int64_t)Skv * D;
+                int64_t j0 = i - (window - 1);
+                if (j0 < 0) j0 = 0;
+                int64_t j1 = i < Skv - 1 ? i : Skv - 1; /* inclusive */
+                for (int d = 0; d < D; ++d) oacc[d] = 0.f;
+                if (j1 < j0) {
+                    if (o)
+                        for (int d = 0; d < D; ++d) o[((b * Hq + h) * Sq + i) * D + d] = 0;
+                    if (lse) lse[(b * Hq + h) * Sq + i] = logf(fmaxf(sink[h], 1.0e-9f));
+                    continue;
+                }
+                for (int d = 0; d < D; ++d) qf[d] = bf16_to_f32(qrow[d]);
+                float rmax = -INFINITY;
+                for (int64_t j = j0; j <= j1; ++j) {
+                    float acc = 0.f;
+                    const uint16_t* kr = kb + j * D;
+                    for (int d = 0; d < D; ++d) acc += qf[d] * bf16_to_f32(kr[d]);
+                    sc[j - j0] = acc * scale;
+                    rmax = fmaxf(rmax, sc[j - j0]);
+                }
+                float sum = 0.f;
+                for (int64_t j = j0; j <= j1; ++j) {
+                    sc[j - j0] = expf(sc[j - j0] - rmax);
+                    sum += sc[j - j0];
+                }
+                const float denom = sum + sink[h] * expf(-rmax);
+                for (int64_t j = j0; j <= j1; ++j) {
+                    const float p = sc[j - j0] / denom;
+                    const uint16_t* vr = vb + j * D;
+                    for (int d = 0; d < D; ++d) oacc[d] += p * bf16_to_f32(vr[d]);
+                }
+                if (o)
+                    for (int d = 0; d < D; ++d) o[((b * Hq + h) * Sq + i) * D + d] = f32_to_bf16(oacc[d]);
+                if (lse) lse[(b * Hq + h) * Sq + i] = logf(denom) + rmax;
+            }
+        }
+        free(sc);
+        free(oacc);
+        free(qf);
+    }
+    return failed ? -2 : 0;
+}

@@ -9,6 +9,8 @@ It imports, unmodified,
     (tiled, non-causal, any number of query rows), and
   * ``flash_gqa_forward_reference``  examples/python/Triton/test_flash_gqa_kernel.py:27-94
     (full softmax, causal, returns the log-sum-exp),
+  * ``flash_swa_forward_reference``  examples/python/Triton/test_flash_swa_kernel.py:28-118
+    (sliding window + sink term),
 feeds them small seeded N(0,1) bf16 tensors and stores inputs and outputs (bf16 as uint16 bit
 patterns) in ``gqa_golden.npz``.  The tests compare both the C oracle and the CUDA kernels with
 these files, so the oracle is pinned to upstream's own code rather than to itself.
@@ -67,6 +69,25 @@ def main():
         o, lse = flash_gqa_forward_reference(q, k, v, return_lse=True)
         out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
         out[name + "/lse"] = lse.numpy().astype(np.float32)
+        meta.append(name)
+
+    # --- sliding window + sink (upstream un-batched [H,S,D]; reference of test_flash_swa_kernel.py:28-118) ---
+    from test_flash_swa_kernel import flash_swa_forward_reference  # noqa: E402
+    swa_cases = [
+        ("swa_g4_w48", 4, 1, 160, 48),
+        ("swa_g2_w130", 2, 1, 260, 130),
+    ]
+    for i, (name, Hq, Hkv, S, window) in enumerate(swa_cases):
+        g = torch.Generator().manual_seed(3000 + i)
+        q = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        sink = torch.rand(Hq, generator=g) * 2.0 + 0.1
+        o, lse = flash_swa_forward_reference(q, k, v, return_lse=True, window_size=window, sink_value=sink)
+        out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
+        out[name + "/sink"] = sink.numpy().astype(np.float32)
+        out[name + "/window"] = np.array(window)
         meta.append(name)
 
     out["cases"] = np.array(meta)

@@ -38,6 +38,7 @@ def lib():
         _lib.cllo_oracle_gqa_combine.restype = ctypes.c_int
         _lib.cllo_oracle_gqa_prefill_bf16.restype = ctypes.c_int
         _lib.cllo_oracle_num_threads.restype = ctypes.c_int
+        _lib.cllo_oracle_swa_prefill_bf16.restype = ctypes.c_int
     return _lib
 
 
@@ -117,6 +118,22 @@ def prefill(q, k, v, scale, causal, row_begin=0, row_end=None):
         _ptr(q, ctypes.c_uint16), _ptr(k, ctypes.c_uint16), _ptr(v, ctypes.c_uint16), ctypes.c_float(scale),
         1 if causal else 0, _ptr(o, ctypes.c_uint16), _ptr(lse, ctypes.c_float),
         B, Sq, Skv, Hq, Hkv, D, row_begin, row_end)
+    assert rc == 0, rc
+    return o, lse
+
+
+def swa_prefill(q, k, v, scale, window, sink):
+    """Sliding-window + sink forward: q [B,Hq,Sq,D], k,v [B,Hkv,Skv,D] uint16, sink [Hq] fp32 -> (o bits, lse)."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v))
+    sink = np.ascontiguousarray(sink, dtype=np.float32)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    o = np.zeros((B, Hq, Sq, D), dtype=np.uint16)
+    lse = np.zeros((B, Hq, Sq), dtype=np.float32)
+    rc = lib().cllo_oracle_swa_prefill_bf16(
+        _ptr(q, ctypes.c_uint16), _ptr(k, ctypes.c_uint16), _ptr(v, ctypes.c_uint16), ctypes.c_float(scale),
+        int(window), _ptr(sink, ctypes.c_float), _ptr(o, ctypes.c_uint16), _ptr(lse, ctypes.c_float),
+        B, Sq, Skv, Hq, Hkv, D)
     assert rc == 0, rc
     return o, lse
 

@@ -183,3 +183,30 @@ def test_headline_shape_sampled_units_and_split_invariance():
         want = ol.decode(qs, ks, vs, SCALE, 0)
         ol.assert_parity(a[b:b + 1, h * 16:(h + 1) * 16], want, "unit (%d,%d)" % (b, h))
     assert_clean_status()
+
+
+def test_exchange_kernel_with_a_world_of_one():
+    """The peer exchange+combine kernel with world = 1 (its own buffers as the only peer): must equal the plain
+    normalisation of the local partial, call after call (epoch 0 = count launches on the device)."""
+    import ctypes
+    import cuda_llm_ops_b200 as ops
+    from cuda_llm_ops_b200 import _lib
+    B, S, Hq, Hkv = 1, 900, 16, 2
+    q = ol.randn_bf16((B, Hq, 128), 81)
+    k = ol.randn_bf16((B, Hkv, S, 128), 82)
+    v = ol.randn_bf16((B, Hkv, S, 128), 83)
+    part = torch.zeros((B, Hq, 130), dtype=torch.float32, device="cuda")
+    ops.gqa_decode(to_dev(q), to_dev(k), to_dev(v), scale=SCALE, kv_layout=1, partial_out=part)
+    rows = B * Hq
+    buf = torch.zeros(2 * 1 * rows * 130 + 64, dtype=torch.float32, device="cuda")
+    arr = ctypes.c_void_p * 1
+    gather, flags = arr(buf.data_ptr()), arr(buf.data_ptr() + 2 * rows * 130 * 4)
+    want = ol.decode(q, k, v, SCALE, 1)
+    for _ in range(3):
+        out = torch.zeros((B, Hq, 128), dtype=torch.bfloat16, device="cuda")
+        rc = _lib.load().cllo_gqa_exchange_combine_bf16(part.data_ptr(), gather, flags, 0, 1, 0, out.data_ptr(), rows, 128,
+                                                        None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ol.assert_parity(to_bits(out), want, "exchange world=1")
+    assert_clean_status()

@@ -50,6 +50,24 @@ def test_prefill_oracle_matches_upstream_torch_oracle(golden, name, causal):
         assert np.allclose(got_lse[0], want_lse, atol=2e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["swa_g4_w48", "swa_g2_w130"])
+def test_swa_oracle_matches_upstream_torch_oracle(golden, name):
+    q, k, v, o = (golden[name + "/" + t][None] for t in ("q", "k", "v", "o"))
+    got_o, got_lse = ol.swa_prefill(q, k, v, SCALE, int(golden[name + "/window"]), golden[name + "/sink"])
+    mx, mean, rel = ol.errors(got_o, o)
+    assert mx <= 4e-3 and mean <= 2e-4 and rel <= 4e-3, (mx, mean, rel)
+    assert np.allclose(got_lse[0], golden[name + "/lse"], atol=2e-5, rtol=1e-5)
+
+
+def test_swa_oracle_with_a_window_wider_than_the_sequence_is_causal_attention_plus_sink():
+    q = ol.randn_bf16((1, 2, 50, 128), 14)
+    k = ol.randn_bf16((1, 1, 50, 128), 15)
+    v = ol.randn_bf16((1, 1, 50, 128), 16)
+    o_swa, lse_swa = ol.swa_prefill(q, k, v, SCALE, 1000, np.zeros(2, dtype=np.float32))
+    o_c, lse_c = ol.prefill(q, k, v, SCALE, True)
+    assert np.array_equal(o_swa, o_c) and np.allclose(lse_swa, lse_c, atol=1e-6)
+
+
 def test_partials_combine_to_full_result():
     B, Hq, Hkv, S = 2, 8, 2, 300
     q = ol.randn_bf16((B, Hq, 128), 1)
