@@ -3,6 +3,7 @@
 #include "gqa_decode.cuh"
 #include "gqa_prefill.cuh"
 #include "gqa_exchange.cuh"
+#include "gqa_backward.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -182,6 +183,15 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
     return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
+}
+
+size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Hq) { return backward::workspace_bytes(B, Sq, Hq); }
+
+int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
+                      float scale, int causal, void* grad_q, void* grad_k, void* grad_v, void* workspace,
+                      size_t workspace_bytes, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+    return backward::launch(q, k, v, o, lse, grad_o, scale, causal, grad_q, grad_k, grad_v, workspace, workspace_bytes, B,
+                            Sq, Skv, Hq, Hkv, D, static_cast<cudaStream_t>(stream));
 }
 
 int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int window_size,

@@ -1,0 +1,594 @@
+// GQA attention backward for sm_100a (tcgen05 / tensor memory), as two kernels without atomics:
+//
+//   bwd_dq_kernel     one block per (batch, query head, 128 query rows); loops over KV tiles.
+//                     S = Q K^T and dP = dO V^T into tensor memory; 256 threads turn them into
+//                     dS = P o (dP - D) * scale with P = exp(scale*S - lse) (no row reduction: the forward
+//                     pass left lse, a small pre-pass leaves D = rowsum(dO o O)); dS goes back to tensor
+//                     memory as bf16 and feeds dQ += dS K as the A operand.
+//   bwd_dkdv_kernel   one block per (batch, kv head, 128 kv rows); loops over all query tiles of all heads
+//                     of the group.  It forms the TRANSPOSED tiles directly, S^T = K Q^T and
+//                     dP^T = V dO^T, so that P^T and dS^T are again A operands in tensor memory for
+//                     dV += P^T dO and dK += dS^T Q: no transposes through shared memory, and dK/dV are
+//                     summed over the heads of the group in the accumulators: one rounding, deterministic.
+//
+// Both recompute S and dP (7 tile products per (q tile, kv tile) instead of the minimal 5); in exchange no
+// gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dQ (384 of 512 columns),
+// dK/dV kernel S^T | dP^T | dV | dK (all 512).  Shared-memory operand layouts, descriptors, TMA boxes and
+// barrier conventions are those of the forward kernel (gqa_prefill.cuh).
+//
+// Upstream: flash_gqa_backward_bf16_kernel, src/python/Triton/flash_gqa_backward_kernel.py:159-310 (one
+// Triton program per (kv block, query head), dQ/dK/dV accumulated with fp32 atomics) and
+// rowwise_dot_o_grad_o_kernel (:16-48).
+#pragma once
+
+#include "gqa_prefill.cuh"
+
+namespace cllo {
+namespace backward {
+
+using prefill::kBM;
+using prefill::kBN;
+using prefill::kD;
+using prefill::kHalfBytes;
+using prefill::kIdescPV;
+using prefill::kIdescQK;
+using prefill::kLog2e;
+using prefill::kTileBytes;
+using prefill::smem_desc;
+using prefill::tc_commit;
+using prefill::tc_fence_after;
+using prefill::tc_fence_before;
+using prefill::tc_mma_ss;
+using prefill::tc_mma_ts;
+using prefill::tmem_alloc;
+using prefill::tmem_dealloc;
+using prefill::tmem_ld32_wait;
+using prefill::tmem_relinquish;
+using prefill::tmem_st32;
+using prefill::tmem_wait_st;
+
+constexpr int kThreads = 320;  // warps 0-7 element-wise (row x half of the columns), 8 TMA, 9 MMA
+constexpr int kStages = 2;
+constexpr int kSmemFixed = 2 * kTileBytes;                      // dQ kernel: Q, dO;  dK/dV kernel: K, V
+constexpr int kSmemStream = kSmemFixed;                         // then [stage][2 tiles]
+constexpr int kSmemVec = kSmemStream + kStages * 2 * kTileBytes;  // dK/dV kernel: lse/D of the query tile, [2][2][128]
+constexpr int kSmemBar = kSmemVec + 2 * 2 * 128 * 4;
+constexpr int kNumBars = 12;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+
+enum : int {
+    SITE_BWD_FIXED = 40,
+    SITE_BWD_STREAM_FULL = 41,
+    SITE_BWD_STREAM_EMPTY = 42,
+    SITE_BWD_S_FULL = 43,
+    SITE_BWD_DS_FULL = 44,
+    SITE_BWD_DRAIN = 45,
+};
+
+struct Params {
+    const float* lse;    // [B,Hq,Sq], natural log units (forward output)
+    const float* delta;  // [B,Hq,Sq], rowsum(dO o O)
+    __nv_bfloat16* dq;   // [B,Hq,Sq,D]
+    __nv_bfloat16* dk;   // [B,Hkv,Skv,D]
+    __nv_bfloat16* dv;   // [B,Hkv,Skv,D]
+    float scale;
+    int B, Sq, Skv, Hq, Hkv, G, causal, n_qt, n_kt;
+};
+
+// tensor-memory column of the A operand for k-step ks when the 128 K-values were written by two
+// warpgroups, each into the first 32 columns of its own 64-column half
+__device__ __forceinline__ uint32_t a_col(int ks) { return static_cast<uint32_t>(ks < 4 ? ks * 8 : 64 + (ks - 4) * 8); }
+
+// D[row] = sum_d dO[row][d] * O[row][d]; one warp per row of 128 dims
+__global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                                        const __nv_bfloat16* __restrict__ grad_o,
+                                                        float* __restrict__ delta, long long rows) {
+    const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint2 a = *reinterpret_cast<const uint2*>(o + row * kD + lane * 4);
+    const uint2 g = *reinterpret_cast<const uint2*>(grad_o + row * kD + lane * 4);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(g2[i]);
+        acc += x.x * y.x + x.y * y.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) delta[row] = acc;
+}
+
+struct Bars {
+    uint32_t base;
+    __device__ uint32_t fixed_full() const { return base; }
+    __device__ uint32_t stream_full(int s) const { return base + 8 * (1 + s); }
+    __device__ uint32_t stream_empty(int s) const { return base + 8 * (3 + s); }
+    __device__ uint32_t aux_empty(int s) const { return base + 8 * (5 + s); }  // dQ kernel: V stage released early
+    __device__ uint32_t s_full() const { return base + 8 * 7; }
+    __device__ uint32_t ds_full() const { return base + 8 * 8; }
+    __device__ uint32_t drain() const { return base + 8 * 9; }
+};
+
+__device__ __forceinline__ void init_bars(const Bars& bars) {
+    mbar_init(bars.fixed_full(), 1);
+    for (int s = 0; s < kStages; ++s) {
+        mbar_init(bars.stream_full(s), 1);
+        mbar_init(bars.stream_empty(s), 1);
+        mbar_init(bars.aux_empty(s), 1);
+    }
+    mbar_init(bars.s_full(), 1);
+    mbar_init(bars.ds_full(), 2 * kBM);
+    mbar_init(bars.drain(), 1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const Bars bars{base + kSmemBar};
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    long long id = blockIdx.x;
+    const int g = static_cast<int>(id % p.G);
+    id /= p.G;
+    const int qt = p.n_qt - 1 - static_cast<int>(id % p.n_qt);  // heavy causal tiles first
+    id /= p.n_qt;
+    const int kvh = static_cast<int>(id % p.Hkv);
+    const int b = static_cast<int>(id / p.Hkv);
+    const int h = kvh * p.G + g;
+    const int q0 = qt * kBM;
+    int n_kv = p.n_kt;
+    if (p.causal) {
+        const int lim = (q0 + kBM - 1) / kBN + 1;
+        n_kv = lim < n_kv ? lim : n_kv;
+    }
+
+    if (threadIdx.x == 0) {
+        init_bars(bars);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;
+    const uint32_t sm_q = base, sm_do = base + kTileBytes;
+    auto sm_k = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes; };
+    auto sm_v = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes + kTileBytes; };
+
+    if (warp == 8) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
+            tma_load_4d(sm_q, &tm_q, bars.fixed_full(), 0, q0, h, b);
+            tma_load_4d(sm_q + kHalfBytes, &tm_q, bars.fixed_full(), 64, q0, h, b);
+            tma_load_4d(sm_do, &tm_do, bars.fixed_full(), 0, q0, h, b);
+            tma_load_4d(sm_do + kHalfBytes, &tm_do, bars.fixed_full(), 64, q0, h, b);
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % kStages;
+                const uint32_t use = static_cast<uint32_t>(j / kStages);
+                // K of a stage is released by the dQ product, V earlier by the dP product
+                mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
+                mbar_wait(bars.aux_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
+                mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
+                tma_load_4d(sm_k(s), &tm_k, bars.stream_full(s), 0, j * kBN, kvh, b);
+                tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.stream_full(s), 64, j * kBN, kvh, b);
+                tma_load_4d(sm_v(s), &tm_v, bars.stream_full(s), 0, j * kBN, kvh, b);
+                tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.stream_full(s), 64, j * kBN, kvh, b);
+            }
+            if (*abort_flag) {
+                for (int j = (n_kv > kStages ? n_kv - kStages : 0); j < n_kv; ++j) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bars.stream_full(j % kStages), static_cast<uint32_t>(j / kStages) & 1u) &&
+                           clock64() - t0 < kWaitLimitCycles / 64) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % kStages;
+                const uint32_t use = static_cast<uint32_t>(j / kStages);
+                mbar_wait(bars.stream_full(s), use & 1u, abort_flag, SITE_BWD_STREAM_FULL, j);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {  // S = Q K^T
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(tm_s, smem_desc(sm_q + off, 16, 1024), smem_desc(sm_k(s) + off, 16, 1024), kIdescQK,
+                              ks > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {  // dP = dO V^T
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(tm_dp, smem_desc(sm_do + off, 16, 1024), smem_desc(sm_v(s) + off, 16, 1024), kIdescQK,
+                              ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bars.s_full());
+                tc_commit(bars.aux_empty(s));
+                mbar_wait(bars.ds_full(), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)  // dQ += dS K   (K tile as the MN-major B operand)
+                    tc_mma_ts(tm_dq, tm_s + a_col(ks), smem_desc(sm_k(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
+                              (j == 0 && ks == 0) ? 0u : 1u);
+                tc_commit(bars.stream_empty(s));
+            }
+            tc_commit(bars.drain());
+            mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 0);
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bars.drain(), 0) && clock64() - t0 < kWaitLimitCycles / 64) {
+                }
+            }
+        }
+    } else {
+        // element-wise: thread = (query row, 64 of the 128 kv columns)
+        const int half = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        const int qi = q0 + row;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool row_ok = qi < p.Sq;
+        const long long vec_idx = (static_cast<long long>(b) * p.Hq + h) * p.Sq + qi;
+        const float lse2 = row_ok ? p.lse[vec_idx] * kLog2e : 0.f;
+        const float drow = row_ok ? p.delta[vec_idx] : 0.f;
+        const float c = p.scale * kLog2e;
+#pragma unroll 1
+        for (int j = 0; j < n_kv; ++j) {
+            mbar_wait(bars.s_full(), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_BWD_S_FULL, j);
+            __syncwarp();
+            tc_fence_after();
+            // columns this row may see in this tile
+            int limit = p.Skv - 1 - j * kBN;
+            if (p.causal) {
+                const int cl = qi - j * kBN;
+                limit = cl < limit ? cl : limit;
+            }
+            uint32_t pk[32];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int col0 = half * 64 + cc * 32;
+                float sv[32], dpv[32];
+                tmem_ld32_wait(tm_s + lane_base + col0, sv);
+                tmem_ld32_wait(tm_dp + lane_base + col0, dpv);
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p0 = fast_exp2(fmaf(sv[e], c, -lse2));
+                    float p1 = fast_exp2(fmaf(sv[e + 1], c, -lse2));
+                    p0 = (col0 + e <= limit) ? p0 : 0.f;
+                    p1 = (col0 + e + 1 <= limit) ? p1 : 0.f;
+                    const float d0 = p0 * (dpv[e] - drow) * p.scale;
+                    const float d1 = p1 * (dpv[e + 1] - drow) * p.scale;
+                    pk[cc * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+                }
+            }
+            // dS (bf16) over the first 32 columns of this warpgroup's own half of S
+            tmem_st32(tm_s + lane_base + half * 64, pk);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bars.ds_full());
+        }
+        // epilogue: dQ -> bf16
+        mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 1);
+        __syncwarp();
+        tc_fence_after();
+        __nv_bfloat16* out = p.dq + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + qi) * kD + half * 64;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+            float ov[32];
+            tmem_ld32_wait(tm_dq + lane_base + half * 64 + cc * 32, ov);
+            if (row_ok) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                    uint4 pkt;
+                    pkt.x = pack_bf16x2(ov[e + 0], ov[e + 1]);
+                    pkt.y = pack_bf16x2(ov[e + 2], ov[e + 3]);
+                    pkt.z = pack_bf16x2(ov[e + 4], ov[e + 5]);
+                    pkt.w = pack_bf16x2(ov[e + 6], ov[e + 7]);
+                    *reinterpret_cast<uint4*>(out + cc * 32 + e) = pkt;
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK, dV
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const Bars bars{base + kSmemBar};
+    float* vec = reinterpret_cast<float*>(gen_base + kSmemVec);  // [parity][0: lse*log2e, 1: delta][128]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    long long id = blockIdx.x;
+    const int jt = static_cast<int>(id % p.n_kt);  // early kv tiles carry the most query tiles when causal
+    id /= p.n_kt;
+    const int kvh = static_cast<int>(id % p.Hkv);
+    const int b = static_cast<int>(id / p.Hkv);
+    const int kv0 = jt * kBN;
+    const int i_lo = p.causal ? kv0 / kBM : 0;  // first query tile that can see this kv tile
+    const int n_i = p.n_qt - i_lo;              // may be <= 0 when Skv > Sq: nothing to accumulate
+    const int n_steps = n_i > 0 ? n_i * p.G : 0;
+
+    if (threadIdx.x == 0) {
+        init_bars(bars);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
+    const uint32_t sm_k = base, sm_v = base + kTileBytes;
+    auto sm_q = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes; };
+    auto sm_do = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes + kTileBytes; };
+
+    if (warp == 8) {
+        if (lane == 0 && n_steps > 0) {
+            mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
+            tma_load_4d(sm_k, &tm_k, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_k + kHalfBytes, &tm_k, bars.fixed_full(), 64, kv0, kvh, b);
+            tma_load_4d(sm_v, &tm_v, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_v + kHalfBytes, &tm_v, bars.fixed_full(), 64, kv0, kvh, b);
+            for (int st = 0; st < n_steps; ++st) {
+                const int s = st % kStages;
+                const uint32_t use = static_cast<uint32_t>(st / kStages);
+                const int h = kvh * p.G + st / n_i;
+                const int qrow0 = (i_lo + st % n_i) * kBM;
+                mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, st);
+                mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
+                tma_load_4d(sm_q(s), &tm_q, bars.stream_full(s), 0, qrow0, h, b);
+                tma_load_4d(sm_q(s) + kHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, h, b);
+                tma_load_4d(sm_do(s), &tm_do, bars.stream_full(s), 0, qrow0, h, b);
+                tma_load_4d(sm_do(s) + kHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, h, b);
+            }
+            if (*abort_flag) {
+                for (int st = (n_steps > kStages ? n_steps - kStages : 0); st < n_steps; ++st) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bars.stream_full(st % kStages), static_cast<uint32_t>(st / kStages) & 1u) &&
+                           clock64() - t0 < kWaitLimitCycles / 64) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0 && n_steps > 0) {
+            mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
+            for (int st = 0; st < n_steps; ++st) {
+                const int s = st % kStages;
+                const uint32_t use = static_cast<uint32_t>(st / kStages);
+                mbar_wait(bars.stream_full(s), use & 1u, abort_flag, SITE_BWD_STREAM_FULL, st);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {  // S^T = K Q^T
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(tm_st, smem_desc(sm_k + off, 16, 1024), smem_desc(sm_q(s) + off, 16, 1024), kIdescQK,
+                              ks > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {  // dP^T = V dO^T
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(tm_dpt, smem_desc(sm_v + off, 16, 1024), smem_desc(sm_do(s) + off, 16, 1024), kIdescQK,
+                              ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bars.s_full());
+                mbar_wait(bars.ds_full(), static_cast<uint32_t>(st) & 1u, abort_flag, SITE_BWD_DS_FULL, st);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)  // dV += P^T dO
+                    tc_mma_ts(tm_dv, tm_st + a_col(ks), smem_desc(sm_do(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
+                              (st == 0 && ks == 0) ? 0u : 1u);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)  // dK += dS^T Q
+                    tc_mma_ts(tm_dk, tm_dpt + a_col(ks), smem_desc(sm_q(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
+                              (st == 0 && ks == 0) ? 0u : 1u);
+                tc_commit(bars.stream_empty(s));
+            }
+            tc_commit(bars.drain());
+            mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 0);
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bars.drain(), 0) && clock64() - t0 < kWaitLimitCycles / 64) {
+                }
+            }
+        }
+    } else {
+        // element-wise: thread = (kv row, 64 of the 128 query columns of the current query tile)
+        const int half = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        const int kvi = kv0 + row;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const int tid = threadIdx.x;  // 0..255 here
+#pragma unroll 1
+        for (int st = 0; st < n_steps; ++st) {
+            const int h = kvh * p.G + st / n_i;
+            const int qrow0 = (i_lo + st % n_i) * kBM;
+            // stage lse*log2e and delta of the 128 query rows of this step (zeros beyond Sq)
+            float* vbuf = vec + (st & 1) * 256;
+            {
+                const int r = tid & 127;
+                const int qr = qrow0 + r;
+                const long long vi = (static_cast<long long>(b) * p.Hq + h) * p.Sq + qr;
+                float val = 0.f;
+                if (qr < p.Sq) val = tid < 128 ? p.lse[vi] * kLog2e : p.delta[vi];
+                vbuf[tid] = val;
+            }
+            named_bar_sync(1, 2 * kBM);
+            mbar_wait(bars.s_full(), static_cast<uint32_t>(st) & 1u, abort_flag, SITE_BWD_S_FULL, st);
+            __syncwarp();
+            tc_fence_after();
+            // query columns that see this kv row: q >= kv (causal) and q < Sq
+            const int first = p.causal ? kvi - qrow0 : 0;
+            const int limit = p.Sq - 1 - qrow0;
+            uint32_t pkp[32], pkd[32];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int col0 = half * 64 + cc * 32;
+                float sv[32], dpv[32];
+                tmem_ld32_wait(tm_st + lane_base + col0, sv);
+                tmem_ld32_wait(tm_dpt + lane_base + col0, dpv);
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int q_a = col0 + e, q_b = col0 + e + 1;
+                    float p0 = fast_exp2(fmaf(sv[e], c, -vbuf[q_a]));
+                    float p1 = fast_exp2(fmaf(sv[e + 1], c, -vbuf[q_b]));
+                    p0 = (q_a >= first && q_a <= limit) ? p0 : 0.f;
+                    p1 = (q_b >= first && q_b <= limit) ? p1 : 0.f;
+                    const float d0 = p0 * (dpv[e] - vbuf[128 + q_a]) * p.scale;
+                    const float d1 = p1 * (dpv[e + 1] - vbuf[128 + q_b]) * p.scale;
+                    pkp[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
+                    pkd[cc * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+                }
+            }
+            tmem_st32(tm_st + lane_base + half * 64, pkp);
+            tmem_st32(tm_dpt + lane_base + half * 64, pkd);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bars.ds_full());
+        }
+        // epilogue: dV, dK -> bf16 (zeros when no query tile reaches this kv tile)
+        if (n_steps > 0) {
+            mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 1);
+            __syncwarp();
+            tc_fence_after();
+        }
+        const bool row_ok = kvi < p.Skv;
+        const long long out_off = ((static_cast<long long>(b) * p.Hkv + kvh) * p.Skv + kvi) * kD + half * 64;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            __nv_bfloat16* out = (which == 0 ? p.dv : p.dk) + out_off;
+            const uint32_t src = (which == 0 ? tm_dv : tm_dk) + lane_base + half * 64;
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                float ov[32];
+                if (n_steps > 0) {
+                    tmem_ld32_wait(src + cc * 32, ov);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) ov[e] = 0.f;
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 pkt;
+                        pkt.x = pack_bf16x2(ov[e + 0], ov[e + 1]);
+                        pkt.y = pack_bf16x2(ov[e + 2], ov[e + 3]);
+                        pkt.z = pack_bf16x2(ov[e + 4], ov[e + 5]);
+                        pkt.w = pack_bf16x2(ov[e + 6], ov[e + 7]);
+                        *reinterpret_cast<uint4*>(out + cc * 32 + e) = pkt;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+static size_t workspace_bytes(int B, int Sq, int Hq) {
+    if (B <= 0 || Sq <= 0 || Hq <= 0) return 0;
+    return static_cast<size_t>(B) * Hq * Sq * sizeof(float);
+}
+
+static int launch(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
+                  float scale, int causal, void* grad_q, void* grad_k, void* grad_v, void* workspace,
+                  size_t workspace_size, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+    if (!q || !k || !v || !o || !lse || !grad_o || !grad_q || !grad_k || !grad_v) return CLLO_E_BAD_ARG;
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return CLLO_E_BAD_ARG;
+    if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
+    const void* ptrs[] = {q, k, v, o, grad_o, grad_q, grad_k, grad_v};
+    for (const void* ptr : ptrs)
+        if (!aligned_to(ptr, 16)) return CLLO_E_BAD_ARG;
+    if (D != kD) return CLLO_E_UNSUPPORTED;
+    if (!workspace || workspace_size < workspace_bytes(B, Sq, Hq) || !aligned_to(workspace, 16)) return CLLO_E_WORKSPACE;
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di);
+    if (rc != CLLO_OK) return rc;
+    if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
+
+    Params p;
+    p.lse = lse;
+    p.delta = static_cast<const float*>(workspace);
+    p.dq = static_cast<__nv_bfloat16*>(grad_q);
+    p.dk = static_cast<__nv_bfloat16*>(grad_k);
+    p.dv = static_cast<__nv_bfloat16*>(grad_v);
+    p.scale = scale;
+    p.B = B;
+    p.Sq = Sq;
+    p.Skv = Skv;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = Hq / Hkv;
+    p.causal = causal ? 1 : 0;
+    p.n_qt = (Sq + kBM - 1) / kBM;
+    p.n_kt = (Skv + kBN - 1) / kBN;
+    const long long rows = static_cast<long long>(B) * Hq * Sq;
+    const long long blocks_dq = static_cast<long long>(B) * Hq * p.n_qt;
+    const long long blocks_kv = static_cast<long long>(B) * Hkv * p.n_kt;
+    if (blocks_dq > 0x7fffffffLL || blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+
+    CUtensorMap tm_q, tm_k, tm_v, tm_do;
+    if ((rc = prefill::encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
+    if ((rc = prefill::encode_bhsd_map(&tm_k, k, B, Hkv, Skv)) != CLLO_OK) return rc;
+    if ((rc = prefill::encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
+    if ((rc = prefill::encode_bhsd_map(&tm_do, grad_o, B, Hq, Sq)) != CLLO_OK) return rc;
+
+    if (!di->backward_attr_set) {
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        di->backward_attr_set = true;
+    }
+    bwd_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(grad_o), static_cast<float*>(workspace),
+        rows);
+    CLLO_CUDA_TRY(cudaGetLastError());
+    bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
+    CLLO_CUDA_TRY(cudaGetLastError());
+    bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
+    CLLO_CUDA_TRY(cudaGetLastError());
+    return CLLO_OK;
+}
+
+}  // namespace backward
+}  // namespace cllo

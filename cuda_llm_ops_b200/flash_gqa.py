@@ -320,6 +320,61 @@ def launch_flash_swa_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None
     return out_b, lse_b
 
 
+def launch_flash_gqa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, causal=True, **_tuning):
+    """Mirror of upstream's backward launcher (src/python/Triton/flash_gqa_backward_kernel.py:312-478).
+
+    3-D or 4-D tensors as the forward launcher; ``lse`` is the forward's fp32 log-sum-exp; returns
+    ``(grad_q, grad_k, grad_v)`` in bf16 with the shapes of q, k, v.  Upstream's Triton tuning keywords are accepted
+    and ignored.
+    """
+    if (q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16
+            or o.dtype != torch.bfloat16 or grad_o.dtype != torch.bfloat16):
+        raise ValueError("Flash GQA backward expects bf16 inputs and grad_o")
+    if lse.dtype != torch.float32:
+        raise ValueError("Flash GQA backward expects lse to be float32")
+    if q.dim() not in (3, 4):
+        raise ValueError("Q must be 3D or 4D")
+    if k.dim() != q.dim() or v.dim() != q.dim() or o.dim() != q.dim() or grad_o.dim() != q.dim():
+        raise ValueError("Q, K, V, O, and grad_o must have matching ranks")
+    squeeze = q.dim() == 3
+    qb, kb, vb, ob, gob = (t.contiguous().unsqueeze(0) if squeeze else t.contiguous() for t in (q, k, v, o, grad_o))
+    lse_b = (lse.contiguous().unsqueeze(0) if squeeze else lse.contiguous())
+    batch, q_heads, seqlen_q, head_dim_qk = qb.shape
+    _, num_kv_heads, seqlen_kv, k_head_dim = kb.shape
+    _, v_heads, v_seqlen, head_dim_v = vb.shape
+    if seqlen_kv != v_seqlen:
+        raise ValueError("K and V must share sequence length")
+    if tuple(ob.shape) != (batch, q_heads, seqlen_q, head_dim_v) or ob.shape != gob.shape:
+        raise ValueError("O and grad_o must have shape [batch, q_heads, seqlen_q, head_dim_v]")
+    if k_head_dim != head_dim_qk:
+        raise ValueError("Q and K must share head_dim_qk")
+    if v_heads != num_kv_heads:
+        raise ValueError("K and V must share number of KV heads")
+    if q_heads % num_kv_heads != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    if tuple(lse_b.shape) != (batch, q_heads, seqlen_q):
+        raise ValueError("LSE must have shape [batch, q_heads, seqlen_q]")
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("grad_o", grad_o)):
+        _require_cuda_bf16(name, t)
+    if head_dim_qk != HEAD_DIM or head_dim_v != HEAD_DIM:
+        raise ValueError("this build supports head_dim == 128 only")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim_qk)
+    grad_q, grad_k, grad_v = torch.empty_like(qb), torch.empty_like(kb), torch.empty_like(vb)
+    lib = _lib.load()
+    with torch.cuda.device(qb.device):
+        nbytes = int(lib.cllo_gqa_bwd_workspace_bytes(batch, seqlen_q, q_heads))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=qb.device)
+        rc = lib.cllo_gqa_bwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), ob.data_ptr(), lse_b.data_ptr(),
+                                   gob.data_ptr(), float(scale), 1 if causal else 0, grad_q.data_ptr(),
+                                   grad_k.data_ptr(), grad_v.data_ptr(), ws.data_ptr(), nbytes, batch, seqlen_q,
+                                   seqlen_kv, q_heads, num_kv_heads, head_dim_qk, _stream_ptr())
+    _lib.check(rc, "cllo_gqa_bwd_bf16")
+    if squeeze:
+        return grad_q.squeeze(0), grad_k.squeeze(0), grad_v.squeeze(0)
+    return grad_q, grad_k, grad_v
+
+
 def device_status():
     """Synchronise and return (status, detail) from ``cllo_device_status``."""
     import ctypes

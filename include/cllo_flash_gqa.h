@@ -164,6 +164,22 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               const float* sink_value, void* o, float* lse,
                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
+/*
+ * GQA attention backward: grad_q, grad_k, grad_v from grad_o, given the forward's inputs, output and lse.
+ * Stands in for flash_gqa_backward_bf16_kernel + rowwise_dot_o_grad_o_kernel +
+ * launch_flash_gqa_backward_bf16_kernel (src/python/Triton/flash_gqa_backward_kernel.py:159-310, :16-48,
+ * :312-478).  Layouts as the forward: q, o, grad_o, grad_q [B,Hq,Sq,D]; k, v, grad_k, grad_v [B,Hkv,Skv,D]
+ * bf16; lse [B,Hq,Sq] fp32 as written by cllo_gqa_prefill_fwd_bf16.  grad_k / grad_v are summed over the
+ * query heads of each group in fp32 and rounded once; no atomics, results are deterministic.
+ * workspace: cllo_gqa_bwd_workspace_bytes(B, Sq, Hq) bytes (one fp32 per query row), 16-byte aligned.
+ */
+size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Hq);
+int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                      const void* grad_o, float scale, int causal,
+                      void* grad_q, void* grad_k, void* grad_v,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -354,3 +354,88 @@ int cllo_oracle_swa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uin
     }
     return failed ? -2 : 0;
 }
+
+/*
+ * GQA attention backward, layout q,o,grad_o,grad_q [B,Hq,Sq,D]; k,v,grad_k,grad_v [B,Hkv,Skv,D] (bf16).
+ *
+ * Follows examples/python/Triton/test_flash_gqa_kernel.py:97-173: probabilities are recomputed from
+ * fp32 scores with a row-max softmax and the causal mask (:152-156; `causal == 0` skips the mask, upstream
+ * is causal-only); grad_p = grad_o V^T (:158); grad_p_dot = rowsum(grad_o o O) (:159);
+ * grad_scores = (grad_p - grad_p_dot) o probs (:160); grad_q = grad_scores K * scale (:162);
+ * grad_k = grad_scores^T Q * scale summed over the heads of the group (:163,168);
+ * grad_v = probs^T grad_o summed over the heads of the group (:164,169); everything fp32, results rounded
+ * to bf16 (:171).
+ */
+int cllo_oracle_gqa_backward_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o,
+                                  const uint16_t* grad_o, float scale, int causal,
+                                  uint16_t* grad_q, uint16_t* grad_k, uint16_t* grad_v,
+                                  int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return -1;
+    if (Hq % Hkv != 0) return -1;
+    const int G = Hq / Hkv;
+    const int64_t units = (int64_t)B * Hkv;
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* dk = (float*)malloc(sizeof(float) * (size_t)Skv * D);
+        float* dv = (float*)malloc(sizeof(float) * (size_t)Skv * D);
+        float* pr = (float*)malloc(sizeof(float) * (size_t)Skv);
+        float* dq = (float*)malloc(sizeof(float) * (size_t)D);
+        if (!dk || !dv || !pr || !dq) {
+#pragma omp atomic write
+            failed = 1;
+        } else {
+#pragma omp for schedule(dynamic, 1)
+            for (int64_t u = 0; u < units; ++u) {
+                const int64_t b = u / Hkv, kvh = u % Hkv;
+                const uint16_t* kb = k + (b * Hkv + kvh) * (int64_t)Skv * D;
+                const uint16_t* vb = v + (b * Hkv + kvh) * (int64_t)Skv * D;
+                for (int64_t x = 0; x < (int64_t)Skv * D; ++x) dk[x] = dv[x] = 0.f;
+                for (int g = 0; g < G; ++g) {
+                    const int64_t h = kvh * G + g;
+                    for (int64_t i = 0; i < Sq; ++i) {
+                        const int64_t ro = ((b * Hq + h) * Sq + i) * D;
+                        int64_t n = Skv;
+                        if (causal && i + 1 < n) n = i + 1;
+                        float rmax = -INFINITY;
+                        for (int64_t j = 0; j < n; ++j) {
+                            float acc = 0.f;
+                            for (int d = 0; d < D; ++d) acc += bf16_to_f32(q[ro + d]) * bf16_to_f32(kb[j * D + d]);
+                            pr[j] = acc * scale;
+                            rmax = fmaxf(rmax, pr[j]);
+                        }
+                        float sum = 0.f;
+                        for (int64_t j = 0; j < n; ++j) {
+                            pr[j] = expf(pr[j] - rmax);
+                            sum += pr[j];
+                        }
+                        float dot = 0.f;
+                        for (int d = 0; d < D; ++d) dot += bf16_to_f32(grad_o[ro + d]) * bf16_to_f32(o[ro + d]);
+                        for (int d = 0; d < D; ++d) dq[d] = 0.f;
+                        for (int64_t j = 0; j < n; ++j) {
+                            const float pj = pr[j] / sum;
+                            float gp = 0.f;
+                            for (int d = 0; d < D; ++d) gp += bf16_to_f32(grad_o[ro + d]) * bf16_to_f32(vb[j * D + d]);
+                            const float gs = (gp - dot) * pj;
+                            for (int d = 0; d < D; ++d) {
+                                dq[d] += gs * bf16_to_f32(kb[j * D + d]);
+                                dk[j * D + d] += gs * bf16_to_f32(q[ro + d]);
+                                dv[j * D + d] += pj * bf16_to_f32(grad_o[ro + d]);
+                            }
+                        }
+                        for (int d = 0; d < D; ++d) grad_q[ro + d] = f32_to_bf16(dq[d] * scale);
+                    }
+                }
+                for (int64_t x = 0; x < (int64_t)Skv * D; ++x) {
+                    grad_k[(b * Hkv + kvh) * (int64_t)Skv * D + x] = f32_to_bf16(dk[x] * scale);
+                    grad_v[(b * Hkv + kvh) * (int64_t)Skv * D + x] = f32_to_bf16(dv[x]);
+                }
+            }
+        }
+        free(dk);
+        free(dv);
+        free(pr);
+        free(dq);
+    }
+    return failed ? -2 : 0;
+}

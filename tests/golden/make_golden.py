@@ -90,6 +90,21 @@ def main():
         out[name + "/window"] = np.array(window)
         meta.append(name)
 
+    # --- backward (upstream flash_gqa_backward_reference, test_flash_gqa_kernel.py:97-173; causal, un-batched) ---
+    from test_flash_gqa_kernel import flash_gqa_backward_reference  # noqa: E402
+    for i, (name, Hq, Hkv, S) in enumerate([("bwd_g2", 2, 1, 144)]):
+        g = torch.Generator().manual_seed(4000 + i)
+        q = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        grad_o = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        o, lse = flash_gqa_forward_reference(q, k, v, return_lse=True)
+        dq, dk, dv = flash_gqa_backward_reference(q, k, v, o, grad_o)
+        for key, t in (("q", q), ("k", k), ("v", v), ("o", o), ("grad_o", grad_o), ("dq", dq), ("dk", dk), ("dv", dv)):
+            out[name + "/" + key] = _bits(t)
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
+        meta.append(name)
+
     out["cases"] = np.array(meta)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gqa_golden.npz")
     np.savez_compressed(path, **out)

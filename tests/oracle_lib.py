@@ -39,6 +39,7 @@ def lib():
         _lib.cllo_oracle_gqa_prefill_bf16.restype = ctypes.c_int
         _lib.cllo_oracle_num_threads.restype = ctypes.c_int
         _lib.cllo_oracle_swa_prefill_bf16.restype = ctypes.c_int
+        _lib.cllo_oracle_gqa_backward_bf16.restype = ctypes.c_int
     return _lib
 
 
@@ -136,6 +137,30 @@ def swa_prefill(q, k, v, scale, window, sink):
         B, Sq, Skv, Hq, Hkv, D)
     assert rc == 0, rc
     return o, lse
+
+
+def backward(q, k, v, o, grad_o, scale, causal):
+    """q,o,grad_o [B,Hq,Sq,D], k,v [B,Hkv,Skv,D] uint16 -> (grad_q, grad_k, grad_v) bits."""
+    q, k, v, o, grad_o = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v, o, grad_o))
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    gq, gk, gv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    u16 = ctypes.c_uint16
+    rc = lib().cllo_oracle_gqa_backward_bf16(_ptr(q, u16), _ptr(k, u16), _ptr(v, u16), _ptr(o, u16), _ptr(grad_o, u16),
+                                             ctypes.c_float(scale), 1 if causal else 0, _ptr(gq, u16), _ptr(gk, u16),
+                                             _ptr(gv, u16), B, Sq, Skv, Hq, Hkv, D)
+    assert rc == 0, rc
+    return gq, gk, gv
+
+
+def assert_grad_parity(got_bits, want_bits, what=""):
+    """Gradients have no fixed scale, so the gate is relative: relative L2 <= 2e-2 (upstream's own metric) and a
+    max-abs error below 2e-2 of the largest reference magnitude."""
+    mx, mean, rel = errors(got_bits, want_bits)
+    ref_max = float(np.abs(bf16_bits_to_f32(want_bits)).max())
+    assert np.isfinite(bf16_bits_to_f32(got_bits)).all(), what + ": non-finite gradient"
+    assert rel <= 2e-2 and mx <= 2e-2 * max(ref_max, 1e-6), "%s: max-abs %.3e (ref max %.3e) rel-L2 %.3e" % (what, mx, ref_max, rel)
+    return mx, mean, rel
 
 
 def errors(got_bits, want_bits):

@@ -68,6 +68,15 @@ def test_swa_oracle_with_a_window_wider_than_the_sequence_is_causal_attention_pl
     assert np.array_equal(o_swa, o_c) and np.allclose(lse_swa, lse_c, atol=1e-6)
 
 
+def test_backward_oracle_matches_upstream_torch_oracle(golden):
+    name = "bwd_g2"
+    t = {key: golden[name + "/" + key][None] for key in ("q", "k", "v", "o", "grad_o", "dq", "dk", "dv")}
+    gq, gk, gv = ol.backward(t["q"], t["k"], t["v"], t["o"], t["grad_o"], SCALE, True)
+    for got, want, what in ((gq, t["dq"], "dq"), (gk, t["dk"], "dk"), (gv, t["dv"], "dv")):
+        mx, mean, rel = ol.errors(got, want)
+        assert rel <= 4e-3, (what, mx, mean, rel)  # two fp32 evaluation orders of the same formula, bf16 outputs
+
+
 def test_partials_combine_to_full_result():
     B, Hq, Hkv, S = 2, 8, 2, 300
     q = ol.randn_bf16((B, Hq, 128), 1)
