@@ -9,6 +9,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
                     (all-gather of per-GPU partials + LSE combine; strong scaling)
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
     prefill_causal  prefill forward, causal, B=8 in total (strong scaling), S=16384, Hq=64, Hkv=8; batch-sharded
+    backward        GQA attention backward (dQ, dK, dV), causal, upstream's shape
     swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
 
 A step is one pass of the hot path over one batch.  `value` is whole-job throughput with inputs
@@ -202,6 +203,25 @@ def run_ours(args, rank, world, local_rank):
                   "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
                   "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
         host_in = [q, k, v]
+    elif wl == "backward":
+        # upstream's backward benchmark shape (README: 3100 us / 55 TFLOPS on an RTX 5080 Laptop), causal
+        B, S, Hq, Hkv = 1, 4096, 16, 1
+        q, k, v = randn_bf16((B, Hq, S, 128)), randn_bf16((B, Hkv, S, 128)), randn_bf16((B, Hkv, S, 128))
+        grad_o = randn_bf16((B, Hq, S, 128))
+        out, lse = ops.launch_flash_gqa_forward_bf16_kernel(q, k, v, causal=True)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.launch_flash_gqa_backward_bf16_kernel(q, k, v, out, lse, grad_o, causal=True)  # noqa: E731
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        # upstream's own FLOP convention: 5 products, halved for causality (test_flash_gqa_kernel.py:362)
+        units_per_rank = float(B * Hq) * (2 * S * S * (3 * 128 + 2 * 128) // 2)
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "gqa_backward_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 3
+        scaling = "weak"
+        config = {"workload": "backward: GQA attention backward, causal, B=1, S=4096, Hq=16, Hkv=1, D=128",
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [q, k, v]
     elif wl in ("prefill_nc", "prefill_causal"):
         causal = wl == "prefill_causal"
         if causal:
@@ -264,7 +284,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl in ("prefill_nc", "swa"):
+    if wl in ("prefill_nc", "swa", "backward"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -358,7 +378,9 @@ def run_ours(args, rank, world, local_rank):
     roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                 "kernel": "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
-                          "which also holds the merge pass and launch gaps" if bound == "hbm" else "prefill_fwd_kernel",
+                          "which also holds the merge pass and launch gaps" if bound == "hbm"
+                          else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
+                                else "prefill_fwd_kernel"),
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
@@ -469,7 +491,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

@@ -185,7 +185,13 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                            static_cast<cudaStream_t>(stream));
 }
 
-size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Hq) { return backward::workspace_bytes(B, Sq, Hq); }
+size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv) {
+    int sm = 1;  // no device visible: size for the finest head split
+    DeviceInfo* di = nullptr;
+    if (current_device_info(&di) == CLLO_OK && di->sm_count > 0) sm = di->sm_count;
+    else sm = 1 << 20;
+    return backward::workspace_bytes(B, Sq, Skv, Hq, Hkv, sm);
+}
 
 int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
                       float scale, int causal, void* grad_q, void* grad_k, void* grad_v, void* workspace,

@@ -10,6 +10,9 @@
 //                     dP^T = V dO^T, so that P^T and dS^T are again A operands in tensor memory for
 //                     dV += P^T dO and dK += dS^T Q: no transposes through shared memory, and dK/dV are
 //                     summed over the heads of the group in the accumulators: one rounding, deterministic.
+//                     When (kv head, kv tile) pairs are too few to fill the GPU (one kv head, short
+//                     sequence) the heads of a group are divided among several blocks; their fp32 partials
+//                     go to the workspace and bwd_reduce_kernel sums them in a fixed order.
 //
 // Both recompute S and dP (7 tile products per (q tile, kv tile) instead of the minimal 5); in exchange no
 // gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dQ (384 of 512 columns),
@@ -71,8 +74,10 @@ struct Params {
     __nv_bfloat16* dq;   // [B,Hq,Sq,D]
     __nv_bfloat16* dk;   // [B,Hkv,Skv,D]
     __nv_bfloat16* dv;   // [B,Hkv,Skv,D]
+    float* dkv_partial;  // head_splits > 1: fp32 [split][2: dV, dK][B,Hkv,Skv,D]
     float scale;
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qt, n_kt;
+    int head_splits;     // the query heads of a group are divided among this many blocks per kv tile
 };
 
 // tensor-memory column of the A operand for k-step ks when the 128 K-values were written by two
@@ -329,6 +334,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     long long id = blockIdx.x;
+    const int split = static_cast<int>(id % p.head_splits);
+    id /= p.head_splits;
     const int jt = static_cast<int>(id % p.n_kt);  // early kv tiles carry the most query tiles when causal
     id /= p.n_kt;
     const int kvh = static_cast<int>(id % p.Hkv);
@@ -336,7 +343,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int kv0 = jt * kBN;
     const int i_lo = p.causal ? kv0 / kBM : 0;  // first query tile that can see this kv tile
     const int n_i = p.n_qt - i_lo;              // may be <= 0 when Skv > Sq: nothing to accumulate
-    const int n_steps = n_i > 0 ? n_i * p.G : 0;
+    const int heads_here = p.G / p.head_splits;  // head_splits divides G
+    const int head0 = kvh * p.G + split * heads_here;
+    const int n_steps = n_i > 0 ? n_i * heads_here : 0;
 
     if (threadIdx.x == 0) {
         init_bars(bars);
@@ -366,7 +375,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int st = 0; st < n_steps; ++st) {
                 const int s = st % kStages;
                 const uint32_t use = static_cast<uint32_t>(st / kStages);
-                const int h = kvh * p.G + st / n_i;
+                const int h = head0 + st / n_i;
                 const int qrow0 = (i_lo + st % n_i) * kBM;
                 mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, st);
                 mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
@@ -435,7 +444,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int tid = threadIdx.x;  // 0..255 here
 #pragma unroll 1
         for (int st = 0; st < n_steps; ++st) {
-            const int h = kvh * p.G + st / n_i;
+            const int h = head0 + st / n_i;
             const int qrow0 = (i_lo + st % n_i) * kBM;
             // stage lse*log2e and delta of the 128 query rows of this step (zeros beyond Sq)
             float* vbuf = vec + (st & 1) * 256;
@@ -488,9 +497,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         const bool row_ok = kvi < p.Skv;
         const long long out_off = ((static_cast<long long>(b) * p.Hkv + kvh) * p.Skv + kvi) * kD + half * 64;
+        const long long tensor_elems = static_cast<long long>(p.B) * p.Hkv * p.Skv * kD;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
             __nv_bfloat16* out = (which == 0 ? p.dv : p.dk) + out_off;
+            float* part = p.head_splits > 1 ? p.dkv_partial + (split * 2LL + which) * tensor_elems + out_off : nullptr;
             const uint32_t src = (which == 0 ? tm_dv : tm_dk) + lane_base + half * 64;
 #pragma unroll 1
             for (int cc = 0; cc < 2; ++cc) {
@@ -501,7 +512,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 32; ++e) ov[e] = 0.f;
                 }
-                if (row_ok) {
+                if (row_ok && part) {  // fp32 partial of this head split; summed by bwd_reduce_kernel
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<float4*>(part + cc * 32 + e) = make_float4(ov[e], ov[e + 1], ov[e + 2], ov[e + 3]);
+                } else if (row_ok) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
                         uint4 pkt;
@@ -523,12 +538,54 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
 }
 
+// Sum of the head splits' fp32 partials -> bf16 dV and dK (fixed order: deterministic).  4 elements per thread.
+__global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* __restrict__ partial, int splits,
+                                                         long long tensor_elems, __nv_bfloat16* __restrict__ dv,
+                                                         __nv_bfloat16* __restrict__ dk) {
+    const long long i4 = (blockIdx.x * 256LL + threadIdx.x) * 4;
+    if (i4 >= 2 * tensor_elems) return;
+    const int which = i4 >= tensor_elems ? 1 : 0;
+    const long long off = i4 - which * tensor_elems;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float4 x = *reinterpret_cast<const float4*>(partial + (s * 2LL + which) * tensor_elems + off);
+        acc.x += x.x;
+        acc.y += x.y;
+        acc.z += x.z;
+        acc.w += x.w;
+    }
+    uint2 pk;
+    pk.x = pack_bf16x2(acc.x, acc.y);
+    pk.y = pack_bf16x2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>((which ? dk : dv) + off) = pk;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
-static size_t workspace_bytes(int B, int Sq, int Hq) {
-    if (B <= 0 || Sq <= 0 || Hq <= 0) return 0;
-    return static_cast<size_t>(B) * Hq * Sq * sizeof(float);
+// With few kv heads and a short sequence there are too few (kv head, kv tile) blocks to fill the GPU; the query
+// heads of a group are then divided among `splits` blocks (a divisor of G) whose fp32 partials are summed.
+static int choose_head_splits(int G, long long kv_blocks, int sm_count) {
+    int splits = 1;
+    for (int d = 1; d <= G; ++d) {
+        if (G % d != 0) continue;
+        splits = d;
+        if (kv_blocks * d >= 2LL * sm_count) break;
+    }
+    return splits;
+}
+
+static size_t delta_bytes(int B, int Sq, int Hq) {
+    return (static_cast<size_t>(B) * Hq * Sq * sizeof(float) + 255) / 256 * 256;
+}
+
+static size_t workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv, int sm_count) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return 0;
+    const long long kv_blocks = static_cast<long long>(B) * Hkv * ((Skv + kBN - 1) / kBN);
+    const int splits = choose_head_splits(Hq / Hkv, kv_blocks, sm_count);
+    size_t bytes = delta_bytes(B, Sq, Hq);
+    if (splits > 1) bytes += static_cast<size_t>(splits) * 2 * B * Hkv * Skv * kD * sizeof(float);
+    return bytes;
 }
 
 static int launch(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
@@ -541,11 +598,12 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     for (const void* ptr : ptrs)
         if (!aligned_to(ptr, 16)) return CLLO_E_BAD_ARG;
     if (D != kD) return CLLO_E_UNSUPPORTED;
-    if (!workspace || workspace_size < workspace_bytes(B, Sq, Hq) || !aligned_to(workspace, 16)) return CLLO_E_WORKSPACE;
     DeviceInfo* di = nullptr;
     int rc = current_device_info(&di);
     if (rc != CLLO_OK) return rc;
     if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
+    if (!workspace || workspace_size < workspace_bytes(B, Sq, Skv, Hq, Hkv, di->sm_count) || !aligned_to(workspace, 256))
+        return CLLO_E_WORKSPACE;
 
     Params p;
     p.lse = lse;
@@ -565,7 +623,12 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     p.n_kt = (Skv + kBN - 1) / kBN;
     const long long rows = static_cast<long long>(B) * Hq * Sq;
     const long long blocks_dq = static_cast<long long>(B) * Hq * p.n_qt;
-    const long long blocks_kv = static_cast<long long>(B) * Hkv * p.n_kt;
+    const long long kv_tiles = static_cast<long long>(B) * Hkv * p.n_kt;
+    p.head_splits = choose_head_splits(p.G, kv_tiles, di->sm_count);
+    p.dkv_partial = p.head_splits > 1
+                        ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + delta_bytes(B, Sq, Hq))
+                        : nullptr;
+    const long long blocks_kv = kv_tiles * p.head_splits;
     if (blocks_dq > 0x7fffffffLL || blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_do;
@@ -587,6 +650,14 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     CLLO_CUDA_TRY(cudaGetLastError());
     bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
+    if (p.head_splits > 1) {
+        const long long tensor_elems = static_cast<long long>(B) * Hkv * Skv * kD;
+        const long long blocks = (2 * tensor_elems / 4 + 255) / 256;
+        if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+        bwd_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,
+                                                                            p.dv, p.dk);
+        CLLO_CUDA_TRY(cudaGetLastError());
+    }
     return CLLO_OK;
 }
 

@@ -363,7 +363,7 @@ def launch_flash_gqa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, c
     grad_q, grad_k, grad_v = torch.empty_like(qb), torch.empty_like(kb), torch.empty_like(vb)
     lib = _lib.load()
     with torch.cuda.device(qb.device):
-        nbytes = int(lib.cllo_gqa_bwd_workspace_bytes(batch, seqlen_q, q_heads))
+        nbytes = int(lib.cllo_gqa_bwd_workspace_bytes(batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=qb.device)
         rc = lib.cllo_gqa_bwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), ob.data_ptr(), lse_b.data_ptr(),
                                    gob.data_ptr(), float(scale), 1 if causal else 0, grad_q.data_ptr(),

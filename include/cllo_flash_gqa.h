@@ -171,9 +171,11 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
  * :312-478).  Layouts as the forward: q, o, grad_o, grad_q [B,Hq,Sq,D]; k, v, grad_k, grad_v [B,Hkv,Skv,D]
  * bf16; lse [B,Hq,Sq] fp32 as written by cllo_gqa_prefill_fwd_bf16.  grad_k / grad_v are summed over the
  * query heads of each group in fp32 and rounded once; no atomics, results are deterministic.
- * workspace: cllo_gqa_bwd_workspace_bytes(B, Sq, Hq) bytes (one fp32 per query row), 16-byte aligned.
+ * workspace: cllo_gqa_bwd_workspace_bytes(...) bytes, 256-byte aligned: one fp32 per query row, plus -- when
+ * there are too few (kv head, kv tile) pairs to fill the GPU and the query heads of a group are therefore
+ * divided among several blocks -- fp32 partial grad_k / grad_v per head split (summed in a fixed order).
  */
-size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Hq);
+size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv);
 int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse,
                       const void* grad_o, float scale, int causal,
                       void* grad_q, void* grad_k, void* grad_v,
