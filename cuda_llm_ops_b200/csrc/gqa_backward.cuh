@@ -49,6 +49,16 @@ using prefill::tmem_ld32_wait;
 using prefill::tmem_relinquish;
 using prefill::tmem_st32;
 using prefill::tmem_wait_st;
+using prefill::add2;
+using prefill::fma2;
+using prefill::pk2;
+using prefill::upk2;
+
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 
 constexpr int kThreads = 320;  // warps 0-7 element-wise (row x half of the columns), 8 TMA, 9 MMA
 constexpr int kStages = 2;
@@ -258,12 +268,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             mbar_wait(bars.s_full(), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_BWD_S_FULL, j);
             __syncwarp();
             tc_fence_after();
-            // columns this row may see in this tile
+            // columns this row may see in this tile (only diagonal and tail tiles need the test)
             int limit = p.Skv - 1 - j * kBN;
             if (p.causal) {
                 const int cl = qi - j * kBN;
                 limit = cl < limit ? cl : limit;
             }
+            const bool need_mask = (j * kBN + kBN > p.Skv) || (p.causal && (j * kBN + kBN - 1 > q0));
+            const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse2, -lse2);
+            const uint64_t sc2 = pk2(p.scale, p.scale), nds2 = pk2(-drow * p.scale, -drow * p.scale);
             uint32_t pk[32];
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
@@ -273,12 +286,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 tmem_ld32_wait(tm_dp + lane_base + col0, dpv);
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float p0 = fast_exp2(fmaf(sv[e], c, -lse2));
-                    float p1 = fast_exp2(fmaf(sv[e + 1], c, -lse2));
-                    p0 = (col0 + e <= limit) ? p0 : 0.f;
-                    p1 = (col0 + e + 1 <= limit) ? p1 : 0.f;
-                    const float d0 = p0 * (dpv[e] - drow) * p.scale;
-                    const float d1 = p1 * (dpv[e + 1] - drow) * p.scale;
+                    float y0, y1;
+                    upk2(fma2(pk2(sv[e], sv[e + 1]), c2, nl2), y0, y1);
+                    float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                    if (need_mask) {
+                        p0 = (col0 + e <= limit) ? p0 : 0.f;
+                        p1 = (col0 + e + 1 <= limit) ? p1 : 0.f;
+                    }
+                    // dS = P * (dP - D) * scale
+                    float d0, d1;
+                    upk2(mul2(pk2(p0, p1), fma2(pk2(dpv[e], dpv[e + 1]), sc2, nds2)), d0, d1);
                     pk[cc * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
                 }
             }
@@ -328,7 +345,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     const Bars bars{base + kSmemBar};
-    float* vec = reinterpret_cast<float*>(gen_base + kSmemVec);  // [parity][0: lse*log2e, 1: delta][128]
+    float* vec = reinterpret_cast<float*>(gen_base + kSmemVec);  // [parity][0: lse*log2e, 1: delta*scale][128]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -453,16 +470,18 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const int qr = qrow0 + r;
                 const long long vi = (static_cast<long long>(b) * p.Hq + h) * p.Sq + qr;
                 float val = 0.f;
-                if (qr < p.Sq) val = tid < 128 ? p.lse[vi] * kLog2e : p.delta[vi];
+                if (qr < p.Sq) val = tid < 128 ? p.lse[vi] * kLog2e : p.delta[vi] * p.scale;
                 vbuf[tid] = val;
             }
             named_bar_sync(1, 2 * kBM);
             mbar_wait(bars.s_full(), static_cast<uint32_t>(st) & 1u, abort_flag, SITE_BWD_S_FULL, st);
             __syncwarp();
             tc_fence_after();
-            // query columns that see this kv row: q >= kv (causal) and q < Sq
+            // query columns that see this kv row: q >= kv (causal) and q < Sq (only edge tiles need the test)
             const int first = p.causal ? kvi - qrow0 : 0;
             const int limit = p.Sq - 1 - qrow0;
+            const bool need_mask = (qrow0 + kBM > p.Sq) || (p.causal && (kv0 + kBN - 1 > qrow0));
+            const uint64_t c2 = pk2(c, c), sc2 = pk2(p.scale, p.scale);
             uint32_t pkp[32], pkd[32];
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
@@ -471,16 +490,27 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tmem_ld32_wait(tm_st + lane_base + col0, sv);
                 tmem_ld32_wait(tm_dpt + lane_base + col0, dpv);
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int q_a = col0 + e, q_b = col0 + e + 1;
-                    float p0 = fast_exp2(fmaf(sv[e], c, -vbuf[q_a]));
-                    float p1 = fast_exp2(fmaf(sv[e + 1], c, -vbuf[q_b]));
-                    p0 = (q_a >= first && q_a <= limit) ? p0 : 0.f;
-                    p1 = (q_b >= first && q_b <= limit) ? p1 : 0.f;
-                    const float d0 = p0 * (dpv[e] - vbuf[128 + q_a]) * p.scale;
-                    const float d1 = p1 * (dpv[e + 1] - vbuf[128 + q_b]) * p.scale;
-                    pkp[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
-                    pkd[cc * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+                for (int e = 0; e < 32; e += 4) {
+                    // lse*log2e and delta*scale of four query columns at a time (same address for the whole warp)
+                    const float4 l4 = *reinterpret_cast<const float4*>(vbuf + col0 + e);
+                    const float4 d4 = *reinterpret_cast<const float4*>(vbuf + 128 + col0 + e);
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        const int q_a = col0 + e + u, q_b = q_a + 1;
+                        const uint64_t nl2 = u == 0 ? pk2(-l4.x, -l4.y) : pk2(-l4.z, -l4.w);
+                        const uint64_t nd2 = u == 0 ? pk2(-d4.x, -d4.y) : pk2(-d4.z, -d4.w);
+                        float y0, y1;
+                        upk2(fma2(pk2(sv[e + u], sv[e + u + 1]), c2, nl2), y0, y1);
+                        float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                        if (need_mask) {
+                            p0 = (q_a >= first && q_a <= limit) ? p0 : 0.f;
+                            p1 = (q_b >= first && q_b <= limit) ? p1 : 0.f;
+                        }
+                        float d0, d1;
+                        upk2(mul2(pk2(p0, p1), fma2(pk2(dpv[e + u], dpv[e + u + 1]), sc2, nd2)), d0, d1);
+                        pkp[cc * 16 + ((e + u) >> 1)] = pack_bf16x2(p0, p1);
+                        pkd[cc * 16 + ((e + u) >> 1)] = pack_bf16x2(d0, d1);
+                    }
                 }
             }
             tmem_st32(tm_st + lane_base + half * 64, pkp);
