@@ -37,7 +37,11 @@ def decode_workspace_bytes(B, S, Hq, Hkv, D=HEAD_DIM, num_workers=0):
 
 
 def _workspace(device, nbytes):
-    """A per-device scratch tensor, grown on demand (torch owns the memory)."""
+    """A per-device scratch tensor, grown on demand (torch owns the memory).
+
+    It is shared by every call on that device that does not bring its own ``workspace``: calls issued on different
+    streams that may overlap on the GPU must each pass their own.
+    """
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
