@@ -196,8 +196,16 @@ size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv) {
 int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
                       float scale, int causal, void* grad_q, void* grad_k, void* grad_v, void* workspace,
                       size_t workspace_bytes, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
-    return backward::launch(q, k, v, o, lse, grad_o, scale, causal, grad_q, grad_k, grad_v, workspace, workspace_bytes, B,
-                            Sq, Skv, Hq, Hkv, D, static_cast<cudaStream_t>(stream));
+    return backward::launch(q, k, v, o, lse, grad_o, scale, causal, 0, grad_q, grad_k, grad_v, workspace, workspace_bytes,
+                            B, Sq, Skv, Hq, Hkv, D, static_cast<cudaStream_t>(stream));
+}
+
+int cllo_swa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
+                      float scale, int window_size, void* grad_q, void* grad_k, void* grad_v, void* workspace,
+                      size_t workspace_bytes, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+    if (window_size <= 0) return CLLO_E_BAD_ARG;
+    return backward::launch(q, k, v, o, lse, grad_o, scale, 1, window_size, grad_q, grad_k, grad_v, workspace,
+                            workspace_bytes, B, Sq, Skv, Hq, Hkv, D, static_cast<cudaStream_t>(stream));
 }
 
 int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int window_size,

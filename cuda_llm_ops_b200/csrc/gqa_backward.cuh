@@ -88,6 +88,7 @@ struct Params {
     float scale;
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qt, n_kt;
     int head_splits;     // the query heads of a group are divided among this many blocks per kv tile
+    int window;          // > 0: sliding window, a query sees kv in [q - (window - 1), q] (implies causal)
 };
 
 // tensor-memory column of the A operand for k-step ks when the 128 K-values were written by two
@@ -162,11 +163,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int b = static_cast<int>(id / p.Hkv);
     const int h = kvh * p.G + g;
     const int q0 = qt * kBM;
-    int n_kv = p.n_kt;
+    // kv tiles [j_lo, j_lo + n_kv) can hold something visible to this block's rows
+    int j_hi = p.n_kt;
     if (p.causal) {
         const int lim = (q0 + kBM - 1) / kBN + 1;
-        n_kv = lim < n_kv ? lim : n_kv;
+        j_hi = lim < j_hi ? lim : j_hi;
     }
+    int j_lo = 0;
+    if (p.window > 0 && q0 - (p.window - 1) > 0) j_lo = (q0 - (p.window - 1)) / kBN;
+    if (j_lo > j_hi - 1) j_lo = j_hi - 1;
+    const int n_kv = j_hi - j_lo;
 
     if (threadIdx.x == 0) {
         init_bars(bars);
@@ -200,10 +206,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
                 mbar_wait(bars.aux_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
                 mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
-                tma_load_4d(sm_k(s), &tm_k, bars.stream_full(s), 0, j * kBN, kvh, b);
-                tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.stream_full(s), 64, j * kBN, kvh, b);
-                tma_load_4d(sm_v(s), &tm_v, bars.stream_full(s), 0, j * kBN, kvh, b);
-                tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.stream_full(s), 64, j * kBN, kvh, b);
+                tma_load_4d(sm_k(s), &tm_k, bars.stream_full(s), 0, (j_lo + j) * kBN, kvh, b);
+                tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.stream_full(s), 64, (j_lo + j) * kBN, kvh, b);
+                tma_load_4d(sm_v(s), &tm_v, bars.stream_full(s), 0, (j_lo + j) * kBN, kvh, b);
+                tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.stream_full(s), 64, (j_lo + j) * kBN, kvh, b);
             }
             if (*abort_flag) {
                 for (int j = (n_kv > kStages ? n_kv - kStages : 0); j < n_kv; ++j) {
@@ -269,12 +275,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             __syncwarp();
             tc_fence_after();
             // columns this row may see in this tile (only diagonal and tail tiles need the test)
-            int limit = p.Skv - 1 - j * kBN;
+            const int kvt0 = (j_lo + j) * kBN;  // first kv position of this tile
+            int limit = p.Skv - 1 - kvt0;
             if (p.causal) {
-                const int cl = qi - j * kBN;
+                const int cl = qi - kvt0;
                 limit = cl < limit ? cl : limit;
             }
-            const bool need_mask = (j * kBN + kBN > p.Skv) || (p.causal && (j * kBN + kBN - 1 > q0));
+            const int first = p.window > 0 ? qi - (p.window - 1) - kvt0 : 0;
+            const bool need_mask = (kvt0 + kBN > p.Skv) || (p.causal && (kvt0 + kBN - 1 > q0)) ||
+                                   (p.window > 0 && (kvt0 < q0 + kBM - 1 - (p.window - 1)));
             const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse2, -lse2);
             const uint64_t sc2 = pk2(p.scale, p.scale), nds2 = pk2(-drow * p.scale, -drow * p.scale);
             uint32_t pk[32];
@@ -290,8 +299,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     upk2(fma2(pk2(sv[e], sv[e + 1]), c2, nl2), y0, y1);
                     float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                     if (need_mask) {
-                        p0 = (col0 + e <= limit) ? p0 : 0.f;
-                        p1 = (col0 + e + 1 <= limit) ? p1 : 0.f;
+                        p0 = (col0 + e <= limit && col0 + e >= first) ? p0 : 0.f;
+                        p1 = (col0 + e + 1 <= limit && col0 + e + 1 >= first) ? p1 : 0.f;
                     }
                     // dS = P * (dP - D) * scale
                     float d0, d1;
@@ -359,7 +368,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int b = static_cast<int>(id / p.Hkv);
     const int kv0 = jt * kBN;
     const int i_lo = p.causal ? kv0 / kBM : 0;  // first query tile that can see this kv tile
-    const int n_i = p.n_qt - i_lo;              // may be <= 0 when Skv > Sq: nothing to accumulate
+    int i_hi = p.n_qt;                          // one past the last one (a window ends it early)
+    if (p.window > 0) {
+        const int lim = (kv0 + kBN - 1 + p.window - 1) / kBM + 1;
+        i_hi = lim < i_hi ? lim : i_hi;
+    }
+    const int n_i = i_hi - i_lo;                // may be <= 0 when Skv > Sq: nothing to accumulate
     const int heads_here = p.G / p.head_splits;  // head_splits divides G
     const int head0 = kvh * p.G + split * heads_here;
     const int n_steps = n_i > 0 ? n_i * heads_here : 0;
@@ -479,8 +493,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_after();
             // query columns that see this kv row: q >= kv (causal) and q < Sq (only edge tiles need the test)
             const int first = p.causal ? kvi - qrow0 : 0;
-            const int limit = p.Sq - 1 - qrow0;
-            const bool need_mask = (qrow0 + kBM > p.Sq) || (p.causal && (kv0 + kBN - 1 > qrow0));
+            int limit = p.Sq - 1 - qrow0;
+            if (p.window > 0) {
+                const int wl = kvi + (p.window - 1) - qrow0;  // last query that still has this kv in its window
+                limit = wl < limit ? wl : limit;
+            }
+            const bool need_mask = (qrow0 + kBM > p.Sq) || (p.causal && (kv0 + kBN - 1 > qrow0)) ||
+                                   (p.window > 0 && (qrow0 + kBM - 1 > kv0 + (p.window - 1)));
             const uint64_t c2 = pk2(c, c), sc2 = pk2(p.scale, p.scale);
             uint32_t pkp[32], pkd[32];
 #pragma unroll
@@ -619,8 +638,9 @@ static size_t workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv, int sm_co
 }
 
 static int launch(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* grad_o,
-                  float scale, int causal, void* grad_q, void* grad_k, void* grad_v, void* workspace,
+                  float scale, int causal, int window, void* grad_q, void* grad_k, void* grad_v, void* workspace,
                   size_t workspace_size, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+    if (window < 0) return CLLO_E_BAD_ARG;
     if (!q || !k || !v || !o || !lse || !grad_o || !grad_q || !grad_k || !grad_v) return CLLO_E_BAD_ARG;
     if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return CLLO_E_BAD_ARG;
     if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
@@ -648,7 +668,8 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     p.Hq = Hq;
     p.Hkv = Hkv;
     p.G = Hq / Hkv;
-    p.causal = causal ? 1 : 0;
+    p.causal = (causal || window > 0) ? 1 : 0;
+    p.window = window;
     p.n_qt = (Sq + kBM - 1) / kBM;
     p.n_kt = (Skv + kBN - 1) / kBN;
     const long long rows = static_cast<long long>(B) * Hq * Sq;

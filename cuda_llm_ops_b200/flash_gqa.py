@@ -331,11 +331,28 @@ def launch_flash_gqa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, c
     ``(grad_q, grad_k, grad_v)`` in bf16 with the shapes of q, k, v.  Upstream's Triton tuning keywords are accepted
     and ignored.
     """
+    return _attention_backward(q, k, v, o, lse, grad_o, scale, causal, 0, "Flash GQA backward")
+
+
+def launch_flash_swa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, window_size=None, **_tuning):
+    """Mirror of upstream's sliding-window backward launcher (src/python/Triton/SWA/flash_swa_backward_kernel.py:323).
+
+    ``lse`` is the log-sum-exp written by ``launch_flash_swa_forward_bf16_kernel`` (it already contains the sink term,
+    which is all the backward needs of it).
+    """
+    if window_size is None:
+        raise ValueError("window_size must be provided")
+    if int(window_size) <= 0:
+        raise ValueError("window_size must be positive")
+    return _attention_backward(q, k, v, o, lse, grad_o, scale, True, int(window_size), "Flash SWA backward")
+
+
+def _attention_backward(q, k, v, o, lse, grad_o, scale, causal, window, what):
     if (q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16
             or o.dtype != torch.bfloat16 or grad_o.dtype != torch.bfloat16):
-        raise ValueError("Flash GQA backward expects bf16 inputs and grad_o")
+        raise ValueError(what + " expects bf16 inputs and grad_o")
     if lse.dtype != torch.float32:
-        raise ValueError("Flash GQA backward expects lse to be float32")
+        raise ValueError(what + " expects lse to be float32")
     if q.dim() not in (3, 4):
         raise ValueError("Q must be 3D or 4D")
     if k.dim() != q.dim() or v.dim() != q.dim() or o.dim() != q.dim() or grad_o.dim() != q.dim():
@@ -369,11 +386,12 @@ def launch_flash_gqa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, c
     with torch.cuda.device(qb.device):
         nbytes = int(lib.cllo_gqa_bwd_workspace_bytes(batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=qb.device)
-        rc = lib.cllo_gqa_bwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), ob.data_ptr(), lse_b.data_ptr(),
-                                   gob.data_ptr(), float(scale), 1 if causal else 0, grad_q.data_ptr(),
-                                   grad_k.data_ptr(), grad_v.data_ptr(), ws.data_ptr(), nbytes, batch, seqlen_q,
-                                   seqlen_kv, q_heads, num_kv_heads, head_dim_qk, _stream_ptr())
-    _lib.check(rc, "cllo_gqa_bwd_bf16")
+        fn = lib.cllo_swa_bwd_bf16 if window > 0 else lib.cllo_gqa_bwd_bf16
+        rc = fn(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), ob.data_ptr(), lse_b.data_ptr(), gob.data_ptr(),
+                float(scale), window if window > 0 else (1 if causal else 0), grad_q.data_ptr(), grad_k.data_ptr(),
+                grad_v.data_ptr(), ws.data_ptr(), nbytes, batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
+                _stream_ptr())
+    _lib.check(rc, "cllo_swa_bwd_bf16" if window > 0 else "cllo_gqa_bwd_bf16")
     if squeeze:
         return grad_q.squeeze(0), grad_k.squeeze(0), grad_v.squeeze(0)
     return grad_q, grad_k, grad_v

@@ -182,6 +182,18 @@ int cllo_gqa_bwd_bf16(const void* q, const void* k, const void* v, const void* o
                       void* workspace, size_t workspace_bytes,
                       int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
+/*
+ * Backward of the sliding-window + sink forward: same kernels and workspace as cllo_gqa_bwd_bf16 with the
+ * window mask; the sink reaches the gradients only through lse (it has no value vector), so it is not an
+ * argument.  Stands in for flash_swa_backward_bf16_kernel + launch_flash_swa_backward_bf16_kernel
+ * (src/python/Triton/SWA/flash_swa_backward_kernel.py).
+ */
+int cllo_swa_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                      const void* grad_o, float scale, int window_size,
+                      void* grad_q, void* grad_k, void* grad_v,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

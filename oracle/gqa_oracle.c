@@ -366,10 +366,10 @@ int cllo_oracle_swa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uin
  * grad_v = probs^T grad_o summed over the heads of the group (:164,169); everything fp32, results rounded
  * to bf16 (:171).
  */
-int cllo_oracle_gqa_backward_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o,
-                                  const uint16_t* grad_o, float scale, int causal,
-                                  uint16_t* grad_q, uint16_t* grad_k, uint16_t* grad_v,
-                                  int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+static int backward_impl(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o,
+                         const uint16_t* grad_o, float scale, int causal, int window, const float* sink,
+                         uint16_t* grad_q, uint16_t* grad_k, uint16_t* grad_v,
+                         int B, int Sq, int Skv, int Hq, int Hkv, int D) {
     if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return -1;
     if (Hq % Hkv != 0) return -1;
     const int G = Hq / Hkv;
@@ -397,22 +397,29 @@ int cllo_oracle_gqa_backward_bf16(const uint16_t* q, const uint16_t* k, const ui
                         const int64_t ro = ((b * Hq + h) * Sq + i) * D;
                         int64_t n = Skv;
                         if (causal && i + 1 < n) n = i + 1;
+                        int64_t j0 = 0; /* first visible kv position */
+                        if (window > 0 && i - (window - 1) > 0) j0 = i - (window - 1);
+                        for (int d = 0; d < D; ++d) dq[d] = 0.f;
+                        if (j0 >= n) { /* the row sees nothing: no gradient flows through it */
+                            for (int d = 0; d < D; ++d) grad_q[ro + d] = 0;
+                            continue;
+                        }
                         float rmax = -INFINITY;
-                        for (int64_t j = 0; j < n; ++j) {
+                        for (int64_t j = j0; j < n; ++j) {
                             float acc = 0.f;
                             for (int d = 0; d < D; ++d) acc += bf16_to_f32(q[ro + d]) * bf16_to_f32(kb[j * D + d]);
                             pr[j] = acc * scale;
                             rmax = fmaxf(rmax, pr[j]);
                         }
                         float sum = 0.f;
-                        for (int64_t j = 0; j < n; ++j) {
+                        for (int64_t j = j0; j < n; ++j) {
                             pr[j] = expf(pr[j] - rmax);
                             sum += pr[j];
                         }
+                        if (sink) sum += sink[h] * expf(-rmax);
                         float dot = 0.f;
                         for (int d = 0; d < D; ++d) dot += bf16_to_f32(grad_o[ro + d]) * bf16_to_f32(o[ro + d]);
-                        for (int d = 0; d < D; ++d) dq[d] = 0.f;
-                        for (int64_t j = 0; j < n; ++j) {
+                        for (int64_t j = j0; j < n; ++j) {
                             const float pj = pr[j] / sum;
                             float gp = 0.f;
                             for (int d = 0; d < D; ++d) gp += bf16_to_f32(grad_o[ro + d]) * bf16_to_f32(vb[j * D + d]);
@@ -438,4 +445,25 @@ int cllo_oracle_gqa_backward_bf16(const uint16_t* q, const uint16_t* k, const ui
         free(dq);
     }
     return failed ? -2 : 0;
+}
+
+int cllo_oracle_gqa_backward_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o,
+                                  const uint16_t* grad_o, float scale, int causal,
+                                  uint16_t* grad_q, uint16_t* grad_k, uint16_t* grad_v,
+                                  int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+    return backward_impl(q, k, v, o, grad_o, scale, causal, 0, NULL, grad_q, grad_k, grad_v, B, Sq, Skv, Hq, Hkv, D);
+}
+
+/*
+ * Backward of the sliding-window + sink forward.  Follows examples/python/Triton/test_flash_swa_kernel.py:121-220:
+ * the same formulas as the plain backward with the window mask (kv in [i - (window - 1), i]) and the sink term
+ * sink[h] * exp(-rowmax) added to the softmax denominator; the sink has no value vector, so it only scales the
+ * probabilities.
+ */
+int cllo_oracle_swa_backward_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o,
+                                  const uint16_t* grad_o, float scale, int window, const float* sink,
+                                  uint16_t* grad_q, uint16_t* grad_k, uint16_t* grad_v,
+                                  int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+    if (window <= 0 || !sink) return -1;
+    return backward_impl(q, k, v, o, grad_o, scale, 1, window, sink, grad_q, grad_k, grad_v, B, Sq, Skv, Hq, Hkv, D);
 }

@@ -105,6 +105,24 @@ def main():
         out[name + "/lse"] = lse.numpy().astype(np.float32)
         meta.append(name)
 
+    # --- sliding-window backward (upstream flash_swa_backward_reference, test_flash_swa_kernel.py:121-220) ---
+    from test_flash_swa_kernel import flash_swa_backward_reference  # noqa: E402
+    for i, (name, Hq, Hkv, S, window) in enumerate([("swa_bwd_g2_w100", 2, 1, 176, 100)]):
+        g = torch.Generator().manual_seed(5000 + i)
+        q = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        grad_o = torch.randn(Hq, S, 128, generator=g).to(torch.bfloat16)
+        sink = torch.rand(Hq, generator=g) * 2.0 + 0.1
+        o, lse = flash_swa_forward_reference(q, k, v, return_lse=True, window_size=window, sink_value=sink)
+        dq, dk, dv = flash_swa_backward_reference(q, k, v, o, grad_o, window_size=window, sink_value=sink)
+        for key, t in (("q", q), ("k", k), ("v", v), ("o", o), ("grad_o", grad_o), ("dq", dq), ("dk", dk), ("dv", dv)):
+            out[name + "/" + key] = _bits(t)
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
+        out[name + "/sink"] = sink.numpy().astype(np.float32)
+        out[name + "/window"] = np.array(window)
+        meta.append(name)
+
     out["cases"] = np.array(meta)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gqa_golden.npz")
     np.savez_compressed(path, **out)

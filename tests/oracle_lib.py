@@ -40,6 +40,7 @@ def lib():
         _lib.cllo_oracle_num_threads.restype = ctypes.c_int
         _lib.cllo_oracle_swa_prefill_bf16.restype = ctypes.c_int
         _lib.cllo_oracle_gqa_backward_bf16.restype = ctypes.c_int
+        _lib.cllo_oracle_swa_backward_bf16.restype = ctypes.c_int
     return _lib
 
 
@@ -149,6 +150,21 @@ def backward(q, k, v, o, grad_o, scale, causal):
     rc = lib().cllo_oracle_gqa_backward_bf16(_ptr(q, u16), _ptr(k, u16), _ptr(v, u16), _ptr(o, u16), _ptr(grad_o, u16),
                                              ctypes.c_float(scale), 1 if causal else 0, _ptr(gq, u16), _ptr(gk, u16),
                                              _ptr(gv, u16), B, Sq, Skv, Hq, Hkv, D)
+    assert rc == 0, rc
+    return gq, gk, gv
+
+
+def swa_backward(q, k, v, o, grad_o, scale, window, sink):
+    """Sliding-window + sink backward -> (grad_q, grad_k, grad_v) bits."""
+    q, k, v, o, grad_o = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v, o, grad_o))
+    sink = np.ascontiguousarray(sink, dtype=np.float32)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    gq, gk, gv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    u16 = ctypes.c_uint16
+    rc = lib().cllo_oracle_swa_backward_bf16(_ptr(q, u16), _ptr(k, u16), _ptr(v, u16), _ptr(o, u16), _ptr(grad_o, u16),
+                                             ctypes.c_float(scale), int(window), _ptr(sink, ctypes.c_float),
+                                             _ptr(gq, u16), _ptr(gk, u16), _ptr(gv, u16), B, Sq, Skv, Hq, Hkv, D)
     assert rc == 0, rc
     return gq, gk, gv
 

@@ -77,6 +77,16 @@ def test_backward_oracle_matches_upstream_torch_oracle(golden):
         assert rel <= 4e-3, (what, mx, mean, rel)  # two fp32 evaluation orders of the same formula, bf16 outputs
 
 
+def test_swa_backward_oracle_matches_upstream_torch_oracle(golden):
+    name = "swa_bwd_g2_w100"
+    t = {key: golden[name + "/" + key][None] for key in ("q", "k", "v", "o", "grad_o", "dq", "dk", "dv")}
+    gq, gk, gv = ol.swa_backward(t["q"], t["k"], t["v"], t["o"], t["grad_o"], SCALE, int(golden[name + "/window"]),
+                                 golden[name + "/sink"])
+    for got, want, what in ((gq, t["dq"], "dq"), (gk, t["dk"], "dk"), (gv, t["dv"], "dv")):
+        mx, mean, rel = ol.errors(got, want)
+        assert rel <= 4e-3, (what, mx, mean, rel)
+
+
 def test_partials_combine_to_full_result():
     B, Hq, Hkv, S = 2, 8, 2, 300
     q = ol.randn_bf16((B, Hq, 128), 1)

@@ -72,3 +72,36 @@ def test_long_sequence_with_upstream_window_sampled_rows():
         ol.assert_parity(got[:, :, r0:r0 + 32], want_o[:, :, off:off + 32], "rows %d" % r0)
         assert np.allclose(lse.cpu().numpy()[:, :, r0:r0 + 32], want_lse[:, :, off:off + 32], atol=2e-3)
     assert_clean_status()
+
+
+def test_backward_golden_vectors_from_upstream_torch_oracle(golden):
+    import cuda_llm_ops_b200 as ops
+    name = "swa_bwd_g2_w100"
+    t = {key: to_dev(golden[name + "/" + key]) for key in ("q", "k", "v", "o", "grad_o")}
+    lse = torch.from_numpy(golden[name + "/lse"]).cuda()
+    dq, dk, dv = ops.launch_flash_swa_backward_bf16_kernel(t["q"], t["k"], t["v"], t["o"], lse, t["grad_o"],
+                                                           window_size=int(golden[name + "/window"]))
+    torch.cuda.synchronize()
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        ol.assert_grad_parity(to_bits(got), golden[name + "/" + key], key)
+    assert_clean_status()
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,window", [(1, 4, 1, 512, 512, 64), (1, 2, 2, 700, 700, 129), (2, 4, 2, 384, 384, 256),
+                                                    (1, 2, 1, 300, 300, 1), (1, 2, 1, 260, 260, 4096), (1, 2, 1, 400, 200, 100)])
+def test_backward_parity_with_cpu_oracle(B, Hq, Hkv, Sq, Skv, window):
+    import cuda_llm_ops_b200 as ops
+    q = ol.randn_bf16((B, Hq, Sq, 128), 211)
+    k = ol.randn_bf16((B, Hkv, Skv, 128), 212)
+    v = ol.randn_bf16((B, Hkv, Skv, 128), 213)
+    g = ol.randn_bf16((B, Hq, Sq, 128), 214)
+    sink = np.linspace(0.2, 2.0, Hq).astype(np.float32)
+    qd, kd, vd, gd = to_dev(q), to_dev(k), to_dev(v), to_dev(g)
+    o, lse = ops.launch_flash_swa_forward_bf16_kernel(qd, kd, vd, window_size=window, sink_value=torch.from_numpy(sink).cuda())
+    dq, dk, dv = ops.launch_flash_swa_backward_bf16_kernel(qd, kd, vd, o, lse, gd, window_size=window)
+    torch.cuda.synchronize()
+    want = ol.swa_backward(q, k, v, to_bits(o), g, SCALE, window, sink)
+    what = "B%d Hq%d Hkv%d Sq%d Skv%d w%d " % (B, Hq, Hkv, Sq, Skv, window)
+    for got, ref, key in zip((dq, dk, dv), want, ("dq", "dk", "dv")):
+        ol.assert_grad_parity(to_bits(got), ref, what + key)
+    assert_clean_status()
