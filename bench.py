@@ -9,6 +9,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
                     (all-gather of per-GPU partials + LSE combine; strong scaling)
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
     prefill_causal  prefill forward, causal, B=8 in total (strong scaling), S=16384, Hq=64, Hkv=8; batch-sharded
+    rope            rotary position embedding, upstream's shape
     backward        GQA attention backward (dQ, dK, dV), causal, upstream's shape
     swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
 
@@ -203,6 +204,23 @@ def run_ours(args, rank, world, local_rank):
                   "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
                   "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
         host_in = [q, k, v]
+    elif wl == "rope":
+        # upstream's RoPE benchmark shape (README: 510 us / 0.48 "TB/s" on an RTX 5080 Laptop)
+        B, S, hidden = 1, 512 * 1024, 128
+        x = randn_bf16((B, S, hidden))
+        out = torch.empty_like(x)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.LaunchRopeBf16Kernel(x, out, B, S, hidden)  # noqa: E731
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        units_per_rank = 2.0 * B * S * hidden * 2  # read + write, bf16 (same terms as upstream's test_rope.cu:165)
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "rope_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "rope: rotary embedding B=1, S=524288, hidden=128, bf16",
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [x]
     elif wl == "backward":
         # upstream's backward benchmark shape (README: 3100 us / 55 TFLOPS on an RTX 5080 Laptop), causal
         B, S, Hq, Hkv = 1, 4096, 16, 1
@@ -284,7 +302,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl in ("prefill_nc", "swa", "backward"):
+    if wl in ("prefill_nc", "swa", "backward", "rope"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -377,7 +395,7 @@ def run_ours(args, rank, world, local_rank):
     traffic = NCU_TRAFFIC_BYTES.get(wl)
     roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
-                "kernel": "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
+                "kernel": "rope_bf16_kernel" if wl == "rope" else "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
                           "which also holds the merge pass and launch gaps" if bound == "hbm"
                           else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
                                 else "prefill_fwd_kernel"),
@@ -491,7 +509,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

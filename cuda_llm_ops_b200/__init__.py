@@ -9,6 +9,7 @@ from .flash_gqa import (  # noqa: F401
     KV_BSHD,
     PARTIAL_WIDTH,
     LaunchFlashGqaBf16Kernel,
+    LaunchRopeBf16Kernel,
     decode_workspace_bytes,
     device_status,
     gqa_combine,

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "cllo_gqa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "cllo_gqa_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),
+    "cllo_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _f, _vp]),
     "cllo_swa_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_swa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_decode_bf16_noalloc": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),

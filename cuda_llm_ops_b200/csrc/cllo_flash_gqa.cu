@@ -4,6 +4,7 @@
 #include "gqa_prefill.cuh"
 #include "gqa_exchange.cuh"
 #include "gqa_backward.cuh"
+#include "rope.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -183,6 +184,10 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
     return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
+}
+
+int cllo_rope_bf16(const void* input, void* output, int B, int S, int hidden, float base, void* stream) {
+    return rope::launch(input, output, B, S, hidden, base, static_cast<cudaStream_t>(stream));
 }
 
 size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv) {

@@ -397,6 +397,22 @@ def _attention_backward(q, k, v, o, lse, grad_o, scale, causal, window, what):
     return grad_q, grad_k, grad_v
 
 
+def LaunchRopeBf16Kernel(input, output, batchSize, seqLen, hiddenDim, base=10000.0):
+    """Mirror of upstream's C++ RoPE launcher (include/cplusplus/RoPE/rope_kernel.cuh:22), tensors instead of pointers.
+
+    input/output [batchSize, seqLen, hiddenDim] bf16 (the same tensor is allowed).  Like upstream it returns None and
+    does nothing on sizes it refuses (rope_kernel.cu:124-136): non-positive sizes, hiddenDim not a multiple of 8.
+    """
+    if batchSize <= 0 or seqLen <= 0 or hiddenDim <= 0 or hiddenDim % 8 != 0:
+        return
+    _require_cuda_bf16("input", input)
+    _require_cuda_bf16("output", output)
+    with torch.cuda.device(input.device):
+        rc = _lib.load().cllo_rope_bf16(input.data_ptr(), output.data_ptr(), batchSize, seqLen, hiddenDim, float(base),
+                                        _stream_ptr())
+    _lib.check(rc, "cllo_rope_bf16")
+
+
 def device_status():
     """Synchronise and return (status, detail) from ``cllo_device_status``."""
     import ctypes

@@ -194,6 +194,14 @@ int cllo_swa_bwd_bf16(const void* q, const void* k, const void* v, const void* o
                       void* workspace, size_t workspace_bytes,
                       int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
+/*
+ * Rotary position embedding (the step before attention): input/output [B, S, hidden] bf16, interleaved pairs
+ * (2i, 2i+1) rotated by token * base^(-2i/hidden); in place allowed.  Stands in for RopeBf16Kernel +
+ * LaunchRopeBf16Kernel (src/cplusplus/RoPE/rope_kernel.cu:33-107, :117-147; declared in
+ * include/cplusplus/RoPE/rope_kernel.cuh:22).  hidden must be a multiple of 8 and at most 1024.
+ */
+int cllo_rope_bf16(const void* input, void* output, int B, int S, int hidden, float base, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,4 +4,5 @@
 
 #include "FlashGQA/decode_flash_gqa_kernel.cuh"
 #include "FlashGQA/flash_gqa_forward_kernel.cuh"
+#include "RoPE/rope_kernel.cuh"
 #include "Utils/utils.cuh"

@@ -467,3 +467,33 @@ int cllo_oracle_swa_backward_bf16(const uint16_t* q, const uint16_t* k, const ui
     if (window <= 0 || !sink) return -1;
     return backward_impl(q, k, v, o, grad_o, scale, 1, window, sink, grad_q, grad_k, grad_v, B, Sq, Skv, Hq, Hkv, D);
 }
+
+/*
+ * Rotary position embedding over interleaved pairs of the whole hidden dimension.
+ *
+ * Follows examples/cplusplus/test_rope.cu:69-101: invFreq[i] = powf(base, -2 i / hidden) (:79-82); for each
+ * token the fp32 angle token * invFreq[i] (:88), cosf / sinf of that fp32 value (:89-90), and the rotation of
+ * the pair (2i, 2i+1) rounded to bf16 (:95-96).  input/output [B, S, hidden] bf16, hidden even.
+ */
+int cllo_oracle_rope_bf16(const uint16_t* input, uint16_t* output, int B, int S, int hidden, float base) {
+    if (B <= 0 || S <= 0 || hidden <= 0 || (hidden & 1)) return -1;
+    const int half = hidden / 2;
+    float* inv = (float*)malloc(sizeof(float) * (size_t)half);
+    if (!inv) return -2;
+    const float hidden_inv = 1.0f / (float)hidden;
+    for (int i = 0; i < half; ++i) inv[i] = powf(base, -2.0f * (float)i * hidden_inv);
+#pragma omp parallel for schedule(static)
+    for (int64_t bt = 0; bt < (int64_t)B * S; ++bt) {
+        const int token = (int)(bt % S);
+        const int64_t row = bt * hidden;
+        for (int i = 0; i < half; ++i) {
+            const float angle = (float)token * inv[i];
+            const float c = cosf(angle), s = sinf(angle);
+            const float even = bf16_to_f32(input[row + 2 * i]), odd = bf16_to_f32(input[row + 2 * i + 1]);
+            output[row + 2 * i] = f32_to_bf16(even * c - odd * s);
+            output[row + 2 * i + 1] = f32_to_bf16(even * s + odd * c);
+        }
+    }
+    free(inv);
+    return 0;
+}

@@ -1,5 +1,6 @@
-// TEST INFRASTRUCTURE ONLY -- link-time stand-ins that let the upstream benchmark program
-// examples/cplusplus/test_decode_flash_gqa.cu run, unmodified, on a machine without a GPU.
+// TEST INFRASTRUCTURE ONLY -- link-time stand-ins that let the upstream benchmark programs
+// examples/cplusplus/test_decode_flash_gqa.cu and examples/cplusplus/test_rope.cu run, unmodified, on a machine
+// without a GPU.
 //
 // The upstream program fills Q/K/V with random values, runs its CPU reference loop (:184-255),
 // copies the tensors "to the device", calls LaunchFlashGqaBf16Kernel and prints the relative
@@ -24,7 +25,10 @@ extern "C" int cllo_oracle_gqa_decode_bf16(const uint16_t* q, const uint16_t* k,
                                            int Hq, int Hkv, int D, int kv_layout, int s_begin, int s_end, int tile,
                                            int par_heads);
 
+extern "C" int cllo_oracle_rope_bf16(const uint16_t* input, uint16_t* output, int B, int S, int hidden, float base);
+
 static double g_launch_ms = 0.0;
+static bool g_output_cleared = true;  // set by cudaMemset: the next launcher call has to produce the result again
 
 // Replaces the upstream launcher declared in include/cplusplus/FlashGQA/decode_flash_gqa_kernel.cuh:28-38.
 void LaunchFlashGqaBf16Kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, float scale,
@@ -38,6 +42,19 @@ void LaunchFlashGqaBf16Kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, co
         /*par_heads=*/0);
     g_launch_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     std::fprintf(stderr, "[ref_stubs] restated oracle rc=%d, %.3f s\n", rc, g_launch_ms / 1e3);
+}
+
+// Replaces the upstream launcher declared in include/cplusplus/RoPE/rope_kernel.cuh:22 (examples/cplusplus/test_rope.cu
+// calls it 110 times; the restatement runs on the first call and on the first call after the output was cleared).
+void LaunchRopeBf16Kernel(const __nv_bfloat16* input, __nv_bfloat16* output, int batchSize, int seqLen, int hiddenDim,
+                          float base) {
+    if (!g_output_cleared) return;
+    const auto t0 = std::chrono::steady_clock::now();
+    const int rc = cllo_oracle_rope_bf16(reinterpret_cast<const uint16_t*>(input), reinterpret_cast<uint16_t*>(output),
+                                         batchSize, seqLen, hiddenDim, base);
+    g_launch_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    g_output_cleared = false;
+    std::fprintf(stderr, "[ref_stubs] restated rope oracle rc=%d, %.3f s\n", rc, g_launch_ms / 1e3);
 }
 
 extern "C" {
@@ -59,8 +76,16 @@ cudaError_t cudaMemcpy(void* dst, const void* src, size_t n, cudaMemcpyKind) {
 }
 cudaError_t cudaMemset(void* p, int value, size_t n) {
     std::memset(p, value, n);
+    g_output_cleared = true;
     return cudaSuccess;
 }
+cudaError_t cudaFree(void* p) {
+    std::free(p);
+    return cudaSuccess;
+}
+cudaError_t cudaGetLastError(void) { return cudaSuccess; }
+const char* cudaGetErrorString(cudaError_t) { return "stubbed CUDA runtime"; }
+cudaError_t cudaEventDestroy(cudaEvent_t) { return cudaSuccess; }
 cudaError_t cudaEventCreate(cudaEvent_t* e) {
     *e = nullptr;
     return cudaSuccess;

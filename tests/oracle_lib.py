@@ -12,6 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 ORACLE_SO = os.path.join(ORACLE_DIR, "_build", "libgqa_oracle.so")
 REF_BIN = os.path.join(ORACLE_DIR, "_ref", "ref_decode_cpu")
+REF_ROPE_BIN = os.path.join(ORACLE_DIR, "_ref", "ref_rope_cpu")
 
 MAX_ABS_TOL = 2e-2   # parity gate stated for this path: max-abs error of the bf16 output
 MEAN_ABS_TOL = 2e-3  # and mean-abs error, both against the CPU reference on identical inputs
@@ -41,6 +42,7 @@ def lib():
         _lib.cllo_oracle_swa_prefill_bf16.restype = ctypes.c_int
         _lib.cllo_oracle_gqa_backward_bf16.restype = ctypes.c_int
         _lib.cllo_oracle_swa_backward_bf16.restype = ctypes.c_int
+        _lib.cllo_oracle_rope_bf16.restype = ctypes.c_int
     return _lib
 
 
@@ -167,6 +169,16 @@ def swa_backward(q, k, v, o, grad_o, scale, window, sink):
                                              _ptr(gq, u16), _ptr(gk, u16), _ptr(gv, u16), B, Sq, Skv, Hq, Hkv, D)
     assert rc == 0, rc
     return gq, gk, gv
+
+
+def rope(x, base=10000.0):
+    """x [B,S,hidden] uint16 -> rotated bits."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    B, S, hidden = x.shape
+    out = np.zeros_like(x)
+    rc = lib().cllo_oracle_rope_bf16(_ptr(x, ctypes.c_uint16), _ptr(out, ctypes.c_uint16), B, S, hidden, ctypes.c_float(base))
+    assert rc == 0, rc
+    return out
 
 
 def assert_grad_parity(got_bits, want_bits, what=""):
