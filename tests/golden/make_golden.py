@@ -2,7 +2,7 @@
 
 Run once, in a container that has the upstream checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path of the upstream checkout>
 
 It imports, unmodified,
   * ``flash_gqa_reference``          examples/python/Triton/test_decode_flash_gqa_kernel.py:26-79
@@ -29,7 +29,7 @@ def _bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the upstream checkout")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "examples", "python", "Triton"))
     from test_decode_flash_gqa_kernel import flash_gqa_reference  # noqa: E402
