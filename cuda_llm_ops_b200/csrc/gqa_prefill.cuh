@@ -6,15 +6,21 @@
 //     S = Q K^T          tcgen05.mma  M=128 N=128 K=16 x8, Q and K from shared memory (K-major, 128B swizzle)
 //     P = online softmax 128 threads, one query row each, S read from tensor memory with tcgen05.ld
 //     O += P V           tcgen05.mma  M=128 N=128 K=16 x8, P from tensor memory (bf16, written with
-//                        tcgen05.st over the S columns), V from shared memory (MN-major, 128B swizzle)
+//                        tcgen05.st), V from shared memory (MN-major, 128B swizzle)
 // so that the tensor pipe works on one tile while the other tile's softmax runs on the ALUs.
 //
-// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P aliases the first 64
-// columns of its S.  The running maximum is only raised (and O rescaled in tensor memory) when it
-// grew by more than 2^8, which keeps every probability below 256 and makes rescaling rare.
+// Tensor memory (512 columns): P0 (64) | C (128) | P1 (64) | O0 (128) | O1 (128).  Every S = Q K^T of either tile
+// lands in the one region C; the tile's softmax threads copy it to registers at once (about 80 cycles) and hand
+// C back, so the next S -- the other tile's -- can be issued while this tile's softmax is still running, and
+// no S ever waits for the P V product of its own tile.  (With S and P sharing columns, the chain
+// softmax -> P V -> next S -> softmax of one tile was the critical path and left the tensor pipe idle for a
+// quarter of the time.)  The probabilities of tile t live in P_t until P V of that step has retired.
+// The running maximum is only raised (and O rescaled in tensor memory) when it grew by more than 2^8, which
+// keeps every probability below 256 and makes rescaling rare.
 //
-// Warp roles (320 threads): warps 0-3 softmax of tile 0, warps 4-7 softmax of tile 1 (a warp may only
-// touch the 32 tensor-memory lanes given by its index modulo 4), warp 8 TMA producer, warp 9 MMA issuer.
+// Warp roles (384 threads): warps 0-3 softmax of tile 0, warps 4-7 softmax of tile 1 (a warp may only
+// touch the 32 tensor-memory lanes given by its index modulo 4), warp 8 TMA producer, warp 9 MMA issuer,
+// warps 10-11 idle (they complete the third warpgroup so that it can hand registers to the softmax warps).
 // All hand-offs are mbarriers; every wait is bounded and records a status instead of hanging.
 #pragma once
 
@@ -22,6 +28,7 @@
 #include "host_util.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace cllo {
 namespace prefill {
@@ -31,14 +38,24 @@ constexpr int kBM = 128;          // query rows per tile
 constexpr int kBN = 128;          // kv tokens per tile
 constexpr int kTiles = 2;         // query tiles per block
 constexpr int kKvStages = 2;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+// Registers per thread after the warpgroups re-balance themselves (setmaxnreg).  The pool of a block is what it was
+// launched with, kLaunchRegs per thread (the cap that __launch_bounds__(384, 1) gives: 65536 / 384 rounded down to
+// a multiple of 8); asking for more than that in total would block the second softmax warpgroup for ever.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 208;
+constexpr int kOtherRegs = 88;
+static_assert(2 * kSoftmaxRegs + kOtherRegs <= 3 * kLaunchRegs, "setmaxnreg budget exceeds the block's register pool");
+static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0, "setmaxnreg takes multiples of 8");
+// tensor-memory columns
+constexpr uint32_t kColP0 = 0, kColC = 64, kColP1 = 192, kColO = 256;
 constexpr int kHalfBytes = 128 * 128;        // [128 rows][64 dims] bf16 = 16 KB, one swizzled half tile
 constexpr int kTileBytes = 2 * kHalfBytes;   // 32 KB
 constexpr int kSmemQ = 0;
 constexpr int kSmemK = kTiles * kTileBytes;
 constexpr int kSmemV = kSmemK + kKvStages * kTileBytes;
 constexpr int kSmemBar = kSmemV + kKvStages * kTileBytes;
-constexpr int kNumBars = 1 + 4 * kKvStages + 3 * kTiles + 1;
+constexpr int kNumBars = 1 + 4 * kKvStages + 3 + 2 * kTiles + 2;
 constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -55,6 +72,7 @@ enum : int {
     SITE_P_FULL = SITE_PREFILL_BASE + 6,
     SITE_O_FULL = SITE_PREFILL_BASE + 7,
     SITE_DRAIN = SITE_PREFILL_BASE + 8,
+    SITE_C_FREE = SITE_PREFILL_BASE + 9,
 };
 
 struct Params {
@@ -120,6 +138,26 @@ __device__ __forceinline__ void tmem_ld32_wait(uint32_t taddr, float (&r)[32]) {
           "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
           "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
         : "r"(taddr)
+        : "memory");
+}
+// 16 columns + wait, and the matching store (used by the rare rescale of O, where registers are scarce)
+__device__ __forceinline__ void tmem_ld16_wait(uint32_t taddr, uint32_t (&u)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&u)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        ::"r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+          "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+          "r"(taddr)
         : "memory");
 }
 // 128 consecutive fp32 columns of this thread's lane.  The wait is part of the same statement so that no
@@ -250,9 +288,10 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     auto bar_k_empty = [&](int s) { return bar0 + 8 * (1 + kKvStages + s); };
     auto bar_v_full = [&](int s) { return bar0 + 8 * (1 + 2 * kKvStages + s); };
     auto bar_v_empty = [&](int s) { return bar0 + 8 * (1 + 3 * kKvStages + s); };
-    auto bar_s_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + kTiles + t); };
-    auto bar_o_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 2 * kTiles + t); };
+    auto bar_pro = [&](int m) { return bar0 + 8 * (1 + 4 * kKvStages + m); };                   // landings 0..2
+    auto bar_p_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 3 + t); };           // P_t stored
+    auto bar_done = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 3 + kTiles + t); };    // half-step retired
+    const uint32_t bar_c_free = bar0 + 8 * (kNumBars - 2);
     const uint32_t bar_drain = bar0 + 8 * (kNumBars - 1);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
@@ -287,15 +326,16 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_init(bar_q_full, 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(bar_k_full(s), 1);
-            mbar_init(bar_k_empty(s), 1);
+            mbar_init(bar_k_empty(s), kBM);
             mbar_init(bar_v_full(s), 1);
-            mbar_init(bar_v_empty(s), 1);
+            mbar_init(bar_v_empty(s), kBM);
         }
         for (int t = 0; t < kTiles; ++t) {
-            mbar_init(bar_s_full(t), 1);
             mbar_init(bar_p_full(t), kBM);
-            mbar_init(bar_o_full(t), 1);
+            mbar_init(bar_done(t), 1);
         }
+        for (int m = 0; m < 3; ++m) mbar_init(bar_pro(m), 1);
+        mbar_init(bar_c_free, kBM);
         mbar_init(bar_drain, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -309,6 +349,10 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Register budget: the softmax warps hold a whole 128-column row per thread, the copy and MMA warps need
+    // much less.  Each branch below starts with its own setmaxnreg.
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     if (warp == 8) {
         // ------------------------------- TMA producer -------------------------------
         if (lane == 0) {
@@ -349,57 +393,134 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     } else if (warp == 9) {
         // -------------------------------- MMA issuer --------------------------------
-        if (lane == 0) {
-            auto issue_s = [&](int t, int stage) {
-                const uint32_t qa = base + kSmemQ + t * kTileBytes;
-                const uint32_t ka = base + kSmemK + stage * kTileBytes;
+        // Lane 0 issues every tcgen05.mma.  The tensor pipe runs only a couple of instructions behind the issuing
+        // thread, and whatever that thread does between two MMAs (an mbarrier look-up costs well over a hundred
+        // cycles while the pipe saturates the shared-memory port, a commit about as much) is time the pipe idles.
+        // So the work is issued in runs of sixteen MMAs -- O_t += P_t V of the tile that has just finished its
+        // softmax, then the next S for region C -- with ONE look at the barriers before a run (the whole warp looks
+        // at once, one barrier per lane) and ONE commit after it.
+        auto issue_s = [&](int t, int stage) {
+            const uint32_t qa = base + kSmemQ + t * kTileBytes;
+            const uint32_t ka = base + kSmemK + stage * kTileBytes;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tmem_base + t * kBN, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
-                              kIdescQK, ks > 0 ? 1u : 0u);
-                }
-            };
-            auto issue_pv = [&](int t, int stage, bool first) {
-                const uint32_t va = base + kSmemV + stage * kTileBytes;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    tc_mma_ts(tmem_base + 256 + t * kD, tmem_base + t * kBN + ks * 8,
-                              smem_desc(va + ks * 2048, kHalfBytes, 1024), kIdescPV, (first && ks == 0) ? 0u : 1u);
-                }
-            };
-            mbar_wait(bar_q_full, 0, abort_flag, SITE_Q_FULL, 0);
-            mbar_wait(bar_k_full(0), 0, abort_flag, SITE_K_FULL, 0);
-            tc_fence_after();
-            issue_s(0, 0);
-            tc_commit(bar_s_full(0));
-            issue_s(1, 0);
-            tc_commit(bar_s_full(1));
-            tc_commit(bar_k_empty(0));
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j % kKvStages;
-                const uint32_t use = static_cast<uint32_t>(j / kKvStages);
-                const int s1 = (j + 1) % kKvStages;
-                const uint32_t use1 = static_cast<uint32_t>((j + 1) / kKvStages);
-#pragma unroll
-                for (int t = 0; t < kTiles; ++t) {
-                    if (t == 0) mbar_wait(bar_v_full(s), use & 1u, abort_flag, SITE_V_FULL, j);
-                    mbar_wait(bar_p_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_P_FULL, j);
-                    tc_fence_after();
-                    issue_pv(t, s, j == 0);
-                    tc_commit(bar_o_full(t));
-                    if (t == kTiles - 1) tc_commit(bar_v_empty(s));
-                    if (j + 1 < n_kv) {
-                        if (t == 0) {
-                            mbar_wait(bar_k_full(s1), use1 & 1u, abort_flag, SITE_K_FULL, j + 1);
-                            tc_fence_after();
-                        }
-                        issue_s(t, s1);
-                        tc_commit(bar_s_full(t));
-                        if (t == kTiles - 1) tc_commit(bar_k_empty(s1));
-                    }
-                }
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                tc_mma_ss(tmem_base + kColC, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), kIdescQK,
+                          ks > 0 ? 1u : 0u);
             }
+        };
+        auto issue_pv = [&](int t, int stage, bool first) {
+            const uint32_t va = base + kSmemV + stage * kTileBytes;
+            const uint32_t pa = tmem_base + (t ? kColP1 : kColP0);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                tc_mma_ts(tmem_base + kColO + t * kD, pa + ks * 8, smem_desc(va + ks * 2048, kHalfBytes, 1024),
+                          kIdescPV, (first && ks == 0) ? 0u : 1u);
+            }
+        };
+        // "Landing" #m is S of tile (m & 1) at kv step (m >> 1), written to region C.  It may be issued once the
+        // threads of the other tile have copied landing #m-1 out of C (phase m-1 of c_free) and, for tile 0, once
+        // the K tile has arrived.
+        const int n_land = 2 * n_kv;
+        if (lane == 0) {  // the first three landings, nothing to overlap them with
+            mbar_wait(bar_q_full, 0, abort_flag, SITE_Q_FULL, 0);
+            for (int m = 0; m < 3 && m < n_land; ++m) {
+                const int j = m >> 1, st = j % kKvStages;
+                if (m > 0) mbar_wait(bar_c_free, static_cast<uint32_t>(m - 1) & 1u, abort_flag, SITE_C_FREE, m);
+                if ((m & 1) == 0)
+                    mbar_wait(bar_k_full(st), static_cast<uint32_t>(j / kKvStages) & 1u, abort_flag, SITE_K_FULL, j);
+                tc_fence_after();
+                issue_s(m & 1, st);
+                tc_commit(bar_pro(m));
+            }
+        }
+        __syncwarp();
+        // Main part: the two half-steps of a kv step are written out, so that the tile is a compile-time constant and
+        // the choice of barriers needs no branches; the thread that feeds the tensor pipe shares its scheduler with
+        // two softmax warps and every instruction it does not have to issue is time the pipe does not idle.
+        auto half_step = [&](auto tc, int j) {
+            constexpr int t = decltype(tc)::value;   // tile that has finished its softmax
+            const int s = j & 1;                      // stage of V(j), parity of P_t(j)
+            const int sm = t == 0 ? (s ^ 1) : s;      // stage of the K tile of the landing issued here
+            // one barrier per lane: 0 P_t stored, 1 V tile arrived (t = 0), 2 region C free, 3 K tile arrived (t = 1)
+            uint32_t my_bar = bar_p_full(t), my_par = static_cast<uint32_t>(s);
+            if (t == 0 && lane == 1) {
+                my_bar = bar_v_full(s);
+                my_par = static_cast<uint32_t>(j >> 1) & 1u;
+            }
+            if (lane == 2) {
+                my_bar = bar_c_free;
+                my_par = t;
+            }
+            if (t == 1 && lane == 3) {
+                my_bar = bar_k_full(sm);
+                my_par = static_cast<uint32_t>((j + 2) >> 1) & 1u;
+            }
+            if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                if (lane < 4)
+                    mbar_wait(my_bar, my_par, abort_flag,
+                              lane == 0 ? SITE_P_FULL : lane == 2 ? SITE_C_FREE : t == 0 ? SITE_V_FULL : SITE_K_FULL,
+                              2 * j + t);
+                __syncwarp();
+            }
+            if (lane == 0) {
+                tc_fence_after();
+                issue_pv(t, s, j == 0);
+                issue_s(t ^ 1, sm);
+                tc_commit(bar_done(t));
+            }
+            __syncwarp();
+        };
+        using I0 = std::integral_constant<int, 0>;
+        using I1 = std::integral_constant<int, 1>;
+        int j_main = 0;
+#pragma unroll 1
+        for (; j_main + 2 < n_kv; ++j_main) {
+            half_step(I0{}, j_main);
+            half_step(I1{}, j_main);
+        }
+        // the last few half-steps, where landings run out
+#pragma unroll 1
+        for (int n = 2 * j_main; n < n_land; ++n) {
+            // half-step n: tile t has finished the softmax of kv step j
+            const int t = n & 1, j = n >> 1, s = j % kKvStages;
+            const int m = n + 3;  // the landing issued in this half-step
+            const bool has_land = m < n_land;
+            const int jm = m >> 1, sm = jm % kKvStages;
+            // one barrier per lane: 0 P_t stored, 1 V tile arrived, 2 region C free, 3 K tile arrived
+            uint32_t my_bar = bar_p_full(t), my_par = static_cast<uint32_t>(j) & 1u;
+            int my_site = SITE_P_FULL;
+            if (lane == 1 && t == 0) {
+                my_bar = bar_v_full(s);
+                my_par = static_cast<uint32_t>(j / kKvStages) & 1u;
+                my_site = SITE_V_FULL;
+            } else if (lane == 2 && n + 1 < n_land) {
+                // Phase n+2 of c_free (landing n+2 copied out) frees region C for landing m.  It is looked at even
+                // when no landing is left to issue (then the last phase there is, n_land-1): retiring this
+                // half-step advances done[t], and the other tile must have passed its own wait on done[t]'s
+                // previous phase first -- which it has once it has copied its landing out of C.
+                const int q = n + 2 < n_land ? n + 2 : n_land - 1;
+                my_bar = bar_c_free;
+                my_par = static_cast<uint32_t>(q) & 1u;
+                my_site = SITE_C_FREE;
+            } else if (lane == 3 && has_land && (m & 1) == 0) {
+                my_bar = bar_k_full(sm);
+                my_par = static_cast<uint32_t>(jm / kKvStages) & 1u;
+                my_site = SITE_K_FULL;
+            }
+            if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                if (lane < 4) mbar_wait(my_bar, my_par, abort_flag, my_site, n);
+                __syncwarp();
+            }
+            if (lane == 0) {
+                tc_fence_after();
+                issue_pv(t, s, j == 0);
+                if (has_land) issue_s(m & 1, sm);
+                tc_commit(bar_done(t));
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
             // everything issued must have retired before tensor memory is released
             tc_commit(bar_drain);
             mbar_wait(bar_drain, 0, abort_flag, SITE_DRAIN, 0);
@@ -409,23 +530,39 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 }
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         // ------------------------- softmax + epilogue (one row per thread) -------------------------
         const int t = warp >> 2;
         const int row_in_tile = (warp & 3) * 32 + lane;
         const int qi = q0 + t * kBM + row_in_tile;  // global query row
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + t * kBN;
-        const uint32_t o_addr = tmem_base + lane_base + 256 + t * kD;
+        const uint32_t c_addr = tmem_base + lane_base + kColC;
+        const uint32_t p_addr = tmem_base + lane_base + (t ? kColP1 : kColP0);
+        const uint32_t o_addr = tmem_base + lane_base + kColO + t * kD;
         float m = -INFINITY, l = 0.f;
 
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
-            mbar_wait(bar_s_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_S_FULL, j);
+            {
+                // S of this tile and step is landing #m; landings 0..2 have barriers of their own, landing m >= 3 was
+                // issued in half-step m - 3 and retires with it
+                const int m = 2 * j + t;
+                if (m < 3)
+                    mbar_wait(bar_pro(m), 0, abort_flag, SITE_S_FULL, j);
+                else
+                    mbar_wait(bar_done((m - 3) & 1), static_cast<uint32_t>((m - 3) >> 1) & 1u, abort_flag, SITE_S_FULL, j);
+            }
             __syncwarp();
             tc_fence_after();
             float x[128];
-            tmem_ld128_wait(s_addr, x);
+            tmem_ld128_wait(c_addr, x);
+            // the scores are in registers: hand region C back for the other tile's next S
+            tc_fence_before();
+            mbar_arrive(bar_c_free);
+            // S of tile 1 was the last user of this K tile
+            if (t == kTiles - 1) mbar_arrive(bar_k_empty(j % kKvStages));
 
             // mask (diagonal / tail tiles only), then the row extreme of the RAW scores: the scale is folded
             // into the exponent argument below, y = s * c - m with m kept in scaled log2 units
@@ -457,6 +594,20 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             e2 = neg ? fminf(e2, e3) : fmaxf(e2, e3);
             const float mx = (neg ? fminf(e0, e2) : fmaxf(e0, e2)) * p.scale_log2;
 
+            // P V of the previous step must have retired before O_t is rescaled or P_t overwritten.  It was issued
+            // when this tile's previous softmax ended, so the wait is put as late as possible: inside the (rare)
+            // rescale, otherwise after the exponentials, just before the probabilities are stored.
+            bool pv_retired = (j == 0);
+            auto wait_pv = [&]() {
+                if (!pv_retired) {
+                    mbar_wait(bar_done(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
+                    __syncwarp();
+                    tc_fence_after();
+                    pv_retired = true;
+                    // P V of tile 1 was the last user of the previous V tile
+                    if (t == kTiles - 1) mbar_arrive(bar_v_empty((j - 1) % kKvStages));
+                }
+            };
             // raise the running maximum only when it pays (always on the first tile)
             float alpha = 1.f;
             const bool grow = (j == 0) || (mx > m + kRescaleThreshold);
@@ -465,45 +616,41 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (j > 0) {
                     // a lane taken along by the warp vote may still have seen no visible key (sliding window)
                     alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m - m_new);
-                    mbar_wait(bar_o_full(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
-                    __syncwarp();
-                    tc_fence_after();
+                    wait_pv();
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        float ov[32];
-                        tmem_ld32_wait(o_addr + c * 32, ov);
-                        uint32_t ou[32];
+                    for (int c = 0; c < 8; ++c) {
+                        uint32_t ou[16];
+                        tmem_ld16_wait(o_addr + c * 16, ou);
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) ou[e] = __float_as_uint(ov[e] * alpha);
-                        tmem_st32(o_addr + c * 32, ou);
+                        for (int e = 0; e < 16; ++e) ou[e] = __float_as_uint(__uint_as_float(ou[e]) * alpha);
+                        tmem_st16(o_addr + c * 16, ou);
                     }
                 }
                 m = m_new;
             }
 
-            // probabilities (bf16) into tensor memory over the S columns; row sum from the fp32 values
-            // a row that has not seen a visible key yet (sliding window) still has m = -inf: its scores are all
+            // probabilities (bf16), row sum from the fp32 values.
+            // A row that has not seen a visible key yet (sliding window) still has m = -inf: its scores are all
             // masked, so any finite reference gives the right probabilities (zeros)
             const float m_ref = (m == -INFINITY) ? 0.f : m;
             const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m_ref, -m_ref);
             uint64_t sum2 = pk2(0.f, 0.f);
+            uint32_t pk[64];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pk[32];
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int col = c * 64 + e * 2;
-                    const uint64_t y = fma2(pk2(x[col], x[col + 1]), c2, nm2);
-                    float p0, p1;
-                    if ((e * kEmu8) % 8 < kEmu8)
-                        exp2_pair_fma(y, p0, p1);
-                    else
-                        exp2_pair_sfu(y, p0, p1);
-                    sum2 = add2(sum2, pk2(p0, p1));
-                    pk[e] = pack_bf16x2(p0, p1);
-                }
-                tmem_st32(s_addr + c * 32, pk);
+            for (int e = 0; e < 64; ++e) {
+                const int col = e * 2;
+                const uint64_t y = fma2(pk2(x[col], x[col + 1]), c2, nm2);
+                float p0, p1;
+                if ((e * kEmu8) % 8 < kEmu8)
+                    exp2_pair_fma(y, p0, p1);
+                else
+                    exp2_pair_sfu(y, p0, p1);
+                sum2 = add2(sum2, pk2(p0, p1));
+                pk[e] = pack_bf16x2(p0, p1);
             }
+            wait_pv();
+            tmem_st32(p_addr, *reinterpret_cast<const uint32_t(*)[32]>(&pk[0]));
+            tmem_st32(p_addr + 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[32]));
             float s_lo, s_hi;
             upk2(sum2, s_lo, s_hi);
             l = l * alpha + (s_lo + s_hi);
@@ -513,7 +660,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
 
         // epilogue: O / l -> bf16, lse = m + log(l)
-        mbar_wait(bar_o_full(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
+        mbar_wait(bar_done(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
         __syncwarp();
         tc_fence_after();
         // optional sink term in the denominator; rows without any visible key give zeros
@@ -606,6 +753,17 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
         return (v == 0 || v == 2 || v == 3 || v == 4) ? v : kDefaultEmu8;
     }();
     if (!di->prefill_attr_set) {
+        // the register re-balancing inside the kernel assumes the pool the kernel is launched with: refuse to
+        // launch (rather than block inside setmaxnreg) if the compiler gave the kernel fewer registers
+        const void* fns[4] = {reinterpret_cast<const void*>(prefill_fwd_kernel<0>),
+                              reinterpret_cast<const void*>(prefill_fwd_kernel<2>),
+                              reinterpret_cast<const void*>(prefill_fwd_kernel<3>),
+                              reinterpret_cast<const void*>(prefill_fwd_kernel<4>)};
+        for (const void* fn : fns) {
+            cudaFuncAttributes fa;
+            CLLO_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
+            if (fa.numRegs < kLaunchRegs) return CLLO_E_UNSUPPORTED;
+        }
         CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
