@@ -55,7 +55,7 @@ constexpr int kSmemQ = 0;
 constexpr int kSmemK = kTiles * kTileBytes;
 constexpr int kSmemV = kSmemK + kKvStages * kTileBytes;
 constexpr int kSmemBar = kSmemV + kKvStages * kTileBytes;
-constexpr int kNumBars = 1 + 4 * kKvStages + 3 + 2 * kTiles + 2;
+constexpr int kNumBars = 1 + 4 * kKvStages + 3 * kTiles + 2;
 constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -123,6 +123,32 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same two instructions for the hot loop, taking the LOW words of the shared-memory descriptors (start address
+// and leading-dimension offset; the high word -- stride, version, swizzle -- is one constant) and the accumulate flag
+// as a compile-time constant, so that the issuing thread spends as few instructions as possible between two MMAs.
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+        : "memory");
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
 // 32 columns + wait (see tmem_ld128_wait for why the wait is fused)
@@ -267,6 +293,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
     return static_cast<uint64_t>((addr >> 4) & 0x3fffu) | (static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16) |
            (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
 }
+// The two 32-bit words of that descriptor.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo) {
+    return ((addr >> 4) & 0x3fffu) | (((lbo >> 4) & 0x3fffu) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3fffu) | (1u << 14) | (2u << 29); }
 // Instruction descriptor for kind::f16: fp32 accumulate (bits 4-5 = 1), bf16 A and B (bits 7-9, 10-12 = 1),
 // B major-ness in bit 16 (0 = K-major, 1 = MN-major), N/8 in bits 17-22, M/16 in bits 24-28.
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
@@ -288,9 +319,9 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     auto bar_k_empty = [&](int s) { return bar0 + 8 * (1 + kKvStages + s); };
     auto bar_v_full = [&](int s) { return bar0 + 8 * (1 + 2 * kKvStages + s); };
     auto bar_v_empty = [&](int s) { return bar0 + 8 * (1 + 3 * kKvStages + s); };
-    auto bar_pro = [&](int m) { return bar0 + 8 * (1 + 4 * kKvStages + m); };                   // landings 0..2
-    auto bar_p_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 3 + t); };           // P_t stored
-    auto bar_done = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 3 + kTiles + t); };    // half-step retired
+    auto bar_s_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + t); };               // S_t landed in C
+    auto bar_p_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + kTiles + t); };      // P_t stored
+    auto bar_o_full = [&](int t) { return bar0 + 8 * (1 + 4 * kKvStages + 2 * kTiles + t); };  // P_t V retired
     const uint32_t bar_c_free = bar0 + 8 * (kNumBars - 2);
     const uint32_t bar_drain = bar0 + 8 * (kNumBars - 1);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
@@ -332,9 +363,9 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         for (int t = 0; t < kTiles; ++t) {
             mbar_init(bar_p_full(t), kBM);
-            mbar_init(bar_done(t), 1);
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_o_full(t), 1);
         }
-        for (int m = 0; m < 3; ++m) mbar_init(bar_pro(m), 1);
         mbar_init(bar_c_free, kBM);
         mbar_init(bar_drain, 1);
         *abort_flag = 0;
@@ -396,27 +427,36 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // Lane 0 issues every tcgen05.mma.  The tensor pipe runs only a couple of instructions behind the issuing
         // thread, and whatever that thread does between two MMAs (an mbarrier look-up costs well over a hundred
         // cycles while the pipe saturates the shared-memory port, a commit about as much) is time the pipe idles.
-        // So the work is issued in runs of sixteen MMAs -- O_t += P_t V of the tile that has just finished its
-        // softmax, then the next S for region C -- with ONE look at the barriers before a run (the whole warp looks
-        // at once, one barrier per lane) and ONE commit after it.
+        // So the work is issued in runs of sixteen MMAs -- the next S for region C (the other tile will be waiting for
+        // it before anybody waits for P V), then O_t += P_t V of the tile that has just finished its softmax -- with
+        // ONE look at the barriers before a run (the whole warp looks at once, one barrier per lane).
+        // low descriptor words of the operand tiles (per k step only a constant is added: the tiles are 1024-byte
+        // aligned and no sum leaves the 14-bit address field)
+        const uint32_t hi = smem_desc_hi(1024);
+        const uint32_t q_lo0 = smem_desc_lo(base + kSmemQ, 16), q_lo1 = smem_desc_lo(base + kSmemQ + kTileBytes, 16);
+        const uint32_t k_lo0 = smem_desc_lo(base + kSmemK, 16), k_lo1 = smem_desc_lo(base + kSmemK + kTileBytes, 16);
+        const uint32_t v_lo0 = smem_desc_lo(base + kSmemV, kHalfBytes);
+        const uint32_t v_lo1 = smem_desc_lo(base + kSmemV + kTileBytes, kHalfBytes);
         auto issue_s = [&](int t, int stage) {
-            const uint32_t qa = base + kSmemQ + t * kTileBytes;
-            const uint32_t ka = base + kSmemK + stage * kTileBytes;
+            const uint32_t qa = t ? q_lo1 : q_lo0;
+            const uint32_t ka = stage ? k_lo1 : k_lo0;
+            tc_mma_ss_lo<false>(tmem_base + kColC, qa, ka, hi, kIdescQK);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                tc_mma_ss(tmem_base + kColC, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), kIdescQK,
-                          ks > 0 ? 1u : 0u);
+            for (int ks = 1; ks < 8; ++ks) {
+                const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                tc_mma_ss_lo<true>(tmem_base + kColC, qa + off, ka + off, hi, kIdescQK);
             }
         };
         auto issue_pv = [&](int t, int stage, bool first) {
-            const uint32_t va = base + kSmemV + stage * kTileBytes;
+            const uint32_t va = stage ? v_lo1 : v_lo0;
             const uint32_t pa = tmem_base + (t ? kColP1 : kColP0);
+            const uint32_t oa = tmem_base + kColO + t * kD;
+            if (first)
+                tc_mma_ts_lo<false>(oa, pa, va, hi, kIdescPV);
+            else
+                tc_mma_ts_lo<true>(oa, pa, va, hi, kIdescPV);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                tc_mma_ts(tmem_base + kColO + t * kD, pa + ks * 8, smem_desc(va + ks * 2048, kHalfBytes, 1024),
-                          kIdescPV, (first && ks == 0) ? 0u : 1u);
-            }
+            for (int ks = 1; ks < 8; ++ks) tc_mma_ts_lo<true>(oa, pa + ks * 8, va + ks * (2048 >> 4), hi, kIdescPV);
         };
         // "Landing" #m is S of tile (m & 1) at kv step (m >> 1), written to region C.  It may be issued once the
         // threads of the other tile have copied landing #m-1 out of C (phase m-1 of c_free) and, for tile 0, once
@@ -431,7 +471,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     mbar_wait(bar_k_full(st), static_cast<uint32_t>(j / kKvStages) & 1u, abort_flag, SITE_K_FULL, j);
                 tc_fence_after();
                 issue_s(m & 1, st);
-                tc_commit(bar_pro(m));
+                tc_commit(bar_s_full(m & 1));
             }
         }
         __syncwarp();
@@ -465,9 +505,10 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             if (lane == 0) {
                 tc_fence_after();
+                issue_s(t ^ 1, sm);  // first: the other tile is waiting for it sooner than anybody waits for P V
+                tc_commit(bar_s_full(t ^ 1));
                 issue_pv(t, s, j == 0);
-                issue_s(t ^ 1, sm);
-                tc_commit(bar_done(t));
+                tc_commit(bar_o_full(t));
             }
             __syncwarp();
         };
@@ -494,14 +535,9 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 my_bar = bar_v_full(s);
                 my_par = static_cast<uint32_t>(j / kKvStages) & 1u;
                 my_site = SITE_V_FULL;
-            } else if (lane == 2 && n + 1 < n_land) {
-                // Phase n+2 of c_free (landing n+2 copied out) frees region C for landing m.  It is looked at even
-                // when no landing is left to issue (then the last phase there is, n_land-1): retiring this
-                // half-step advances done[t], and the other tile must have passed its own wait on done[t]'s
-                // previous phase first -- which it has once it has copied its landing out of C.
-                const int q = n + 2 < n_land ? n + 2 : n_land - 1;
+            } else if (lane == 2 && has_land) {
                 my_bar = bar_c_free;
-                my_par = static_cast<uint32_t>(q) & 1u;
+                my_par = static_cast<uint32_t>(m - 1) & 1u;
                 my_site = SITE_C_FREE;
             } else if (lane == 3 && has_land && (m & 1) == 0) {
                 my_bar = bar_k_full(sm);
@@ -514,9 +550,12 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             if (lane == 0) {
                 tc_fence_after();
+                if (has_land) {
+                    issue_s(m & 1, sm);
+                    tc_commit(bar_s_full(m & 1));
+                }
                 issue_pv(t, s, j == 0);
-                if (has_land) issue_s(m & 1, sm);
-                tc_commit(bar_done(t));
+                tc_commit(bar_o_full(t));
             }
             __syncwarp();
         }
@@ -545,15 +584,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
-            {
-                // S of this tile and step is landing #m; landings 0..2 have barriers of their own, landing m >= 3 was
-                // issued in half-step m - 3 and retires with it
-                const int m = 2 * j + t;
-                if (m < 3)
-                    mbar_wait(bar_pro(m), 0, abort_flag, SITE_S_FULL, j);
-                else
-                    mbar_wait(bar_done((m - 3) & 1), static_cast<uint32_t>((m - 3) >> 1) & 1u, abort_flag, SITE_S_FULL, j);
-            }
+            mbar_wait(bar_s_full(t), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_S_FULL, j);
             __syncwarp();
             tc_fence_after();
             float x[128];
@@ -600,7 +631,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             bool pv_retired = (j == 0);
             auto wait_pv = [&]() {
                 if (!pv_retired) {
-                    mbar_wait(bar_done(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
+                    mbar_wait(bar_o_full(t), static_cast<uint32_t>(j - 1) & 1u, abort_flag, SITE_O_FULL, j);
                     __syncwarp();
                     tc_fence_after();
                     pv_retired = true;
@@ -660,7 +691,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
 
         // epilogue: O / l -> bf16, lse = m + log(l)
-        mbar_wait(bar_done(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
+        mbar_wait(bar_o_full(t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag, SITE_O_FULL, n_kv);
         __syncwarp();
         tc_fence_after();
         // optional sink term in the denominator; rows without any visible key give zeros
