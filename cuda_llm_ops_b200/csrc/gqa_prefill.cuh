@@ -151,6 +151,48 @@ __device__ __forceinline__ void tc_mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
+// O += P V (eight MMAs, A from tensor memory) by the leader lane, with a look at an mbarrier (one barrier per
+// lane) put between the fifth and the sixth MMA and its result read only after the eighth.  Memory-pipe
+// instructions of a warp are carried out in order, so a look whose result is needed at once keeps the thread from
+// issuing anything behind it for the whole round trip, and the tensor pipe runs dry; this way the round trip is
+// covered by the last three MMAs.
+__device__ __forceinline__ uint32_t tc_pv_run_with_look(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                                        uint32_t idesc, uint32_t accumulate_first, uint32_t leader,
+                                                        uint32_t look_bar, uint32_t look_parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, pt, q, w;\n\t"
+        ".reg .b64 db;\n\t"
+        ".reg .b32 a, b;\n\t"
+        "setp.ne.b32 p0, %6, 0;\n\t"
+        "setp.ne.b32 q, %7, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], db, %5, p0;\n\t"
+        "add.u32 a, %2, 8;\n\t  add.u32 b, %3, 128;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "add.u32 a, %2, 16;\n\t add.u32 b, %3, 256;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "add.u32 a, %2, 24;\n\t add.u32 b, %3, 384;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "add.u32 a, %2, 32;\n\t add.u32 b, %3, 512;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 w, [%8], %9;\n\t"
+        "add.u32 a, %2, 40;\n\t add.u32 b, %3, 640;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "add.u32 a, %2, 48;\n\t add.u32 b, %3, 768;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "add.u32 a, %2, 56;\n\t add.u32 b, %3, 896;\n\t  mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a], db, %5, pt;\n\t"
+        "selp.u32 %0, 1, 0, w;\n\t"
+        "}"
+        : "=r"(seen)
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate_first), "r"(leader),
+          "r"(look_bar), "r"(look_parity)
+        : "memory");
+    return seen;
+}
 // 32 columns + wait (see tmem_ld128_wait for why the wait is fused)
 __device__ __forceinline__ void tmem_ld32_wait(uint32_t taddr, float (&r)[32]) {
     uint32_t* u = reinterpret_cast<uint32_t*>(r);
@@ -308,7 +350,8 @@ constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 template <int kEmu8>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                   const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -390,6 +433,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
+            tma_prefetch_desc(&tm_o);
             mbar_arrive_expect_tx(bar_q_full, kTiles * kTileBytes);
             for (int t = 0; t < kTiles; ++t) {
                 const uint32_t dst = base + kSmemQ + t * kTileBytes;
@@ -478,47 +522,67 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // Main part: the two half-steps of a kv step are written out, so that the tile is a compile-time constant and
         // the choice of barriers needs no branches; the thread that feeds the tensor pipe shares its scheduler with
         // two softmax warps and every instruction it does not have to issue is time the pipe does not idle.
-        auto half_step = [&](auto tc, int j) {
+        // the barrier a lane looks at before half-step (t, j): 0 P_t stored, 1 V tile arrived (t = 0), 2 region C free,
+        // 3 K tile arrived (t = 1); the other lanes repeat lane 0
+        auto my_barrier = [&](auto tc, int j, uint32_t& bar, uint32_t& par) {
+            constexpr int t = decltype(tc)::value;
+            const int s = j & 1;
+            bar = bar_p_full(t);
+            par = static_cast<uint32_t>(s);
+            if (t == 0 && lane == 1) {
+                bar = bar_v_full(s);
+                par = static_cast<uint32_t>(j >> 1) & 1u;
+            }
+            if (lane == 2) {
+                bar = bar_c_free;
+                par = t;
+            }
+            if (t == 1 && lane == 3) {
+                bar = bar_k_full(s);
+                par = static_cast<uint32_t>((j + 2) >> 1) & 1u;
+            }
+        };
+        using I0 = std::integral_constant<int, 0>;
+        using I1 = std::integral_constant<int, 1>;
+        // `seen`: the look that the previous half-step took at this half-step's barriers came back positive
+        auto half_step = [&](auto tc, int j, bool seen) {
             constexpr int t = decltype(tc)::value;   // tile that has finished its softmax
             const int s = j & 1;                      // stage of V(j), parity of P_t(j)
             const int sm = t == 0 ? (s ^ 1) : s;      // stage of the K tile of the landing issued here
-            // one barrier per lane: 0 P_t stored, 1 V tile arrived (t = 0), 2 region C free, 3 K tile arrived (t = 1)
-            uint32_t my_bar = bar_p_full(t), my_par = static_cast<uint32_t>(s);
-            if (t == 0 && lane == 1) {
-                my_bar = bar_v_full(s);
-                my_par = static_cast<uint32_t>(j >> 1) & 1u;
-            }
-            if (lane == 2) {
-                my_bar = bar_c_free;
-                my_par = t;
-            }
-            if (t == 1 && lane == 3) {
-                my_bar = bar_k_full(sm);
-                my_par = static_cast<uint32_t>((j + 2) >> 1) & 1u;
-            }
-            if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
-                if (lane < 4)
-                    mbar_wait(my_bar, my_par, abort_flag,
-                              lane == 0 ? SITE_P_FULL : lane == 2 ? SITE_C_FREE : t == 0 ? SITE_V_FULL : SITE_K_FULL,
-                              2 * j + t);
-                __syncwarp();
+            uint32_t my_bar, my_par;
+            if (!seen) {
+                my_barrier(tc, j, my_bar, my_par);
+                if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                    if (lane < 4)
+                        mbar_wait(my_bar, my_par, abort_flag,
+                                  lane == 0 ? SITE_P_FULL : lane == 2 ? SITE_C_FREE : t == 0 ? SITE_V_FULL : SITE_K_FULL,
+                                  2 * j + t);
+                    __syncwarp();
+                }
             }
             if (lane == 0) {
                 tc_fence_after();
                 issue_s(t ^ 1, sm);  // first: the other tile is waiting for it sooner than anybody waits for P V
                 tc_commit(bar_s_full(t ^ 1));
-                issue_pv(t, s, j == 0);
-                tc_commit(bar_o_full(t));
             }
             __syncwarp();
+            // the barriers of the next half-step: (1, j) after (0, j), (0, j + 1) after (1, j)
+            if (t == 0)
+                my_barrier(I1{}, j, my_bar, my_par);
+            else
+                my_barrier(I0{}, j + 1, my_bar, my_par);
+            const uint32_t mine = tc_pv_run_with_look(
+                tmem_base + kColO + t * kD, tmem_base + (t ? kColP1 : kColP0), s ? v_lo1 : v_lo0, hi, kIdescPV,
+                j == 0 ? 0u : 1u, lane == 0 ? 1u : 0u, my_bar, my_par);
+            if (lane == 0) tc_commit(bar_o_full(t));
+            return __all_sync(0xffffffffu, mine != 0);
         };
-        using I0 = std::integral_constant<int, 0>;
-        using I1 = std::integral_constant<int, 1>;
         int j_main = 0;
+        bool seen = false;
 #pragma unroll 1
         for (; j_main + 2 < n_kv; ++j_main) {
-            half_step(I0{}, j_main);
-            half_step(I1{}, j_main);
+            seen = half_step(I0{}, j_main, seen);
+            seen = half_step(I1{}, j_main, seen);
         }
         // the last few half-steps, where landings run out
 #pragma unroll 1
@@ -700,22 +764,34 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float denom = l + ((p.sink && visible) ? sink * fast_exp2(-m) : 0.f);
         const float inv_l = visible ? 1.f / denom : 0.f;
         const bool row_ok = qi < p.Sq;
-        __nv_bfloat16* orow = p.o + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + qi) * kD;
+        // O goes out through shared memory and a bulk tensor store: written row by row from the threads, one
+        // store instruction touches 32 different lines and the epilogue is bound by those transactions.  The Q
+        // tile of this query tile is free (every MMA has retired) and has the layout the store expects: two
+        // [128 rows][64 columns] halves, 16-byte chunks of a row XOR-ed with the row index modulo 8.
+        const uint32_t stage_o = base + kSmemQ + t * kTileBytes;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
             float ov[32];
             tmem_ld32_wait(o_addr + c * 32, ov);
-            if (row_ok) {
+            const uint32_t row_base = stage_o + (c >> 1) * kHalfBytes + row_in_tile * 128;
 #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                    uint4 pkt;
-                    pkt.x = pack_bf16x2(ov[e + 0] * inv_l, ov[e + 1] * inv_l);
-                    pkt.y = pack_bf16x2(ov[e + 2] * inv_l, ov[e + 3] * inv_l);
-                    pkt.z = pack_bf16x2(ov[e + 4] * inv_l, ov[e + 5] * inv_l);
-                    pkt.w = pack_bf16x2(ov[e + 6] * inv_l, ov[e + 7] * inv_l);
-                    *reinterpret_cast<uint4*>(orow + c * 32 + e) = pkt;
-                }
+            for (int e = 0; e < 32; e += 8) {
+                const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + (e >> 3));
+                const uint32_t dst = row_base + ((chunk ^ (static_cast<uint32_t>(row_in_tile) & 7u)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                             "r"(pack_bf16x2(ov[e + 0] * inv_l, ov[e + 1] * inv_l)),
+                             "r"(pack_bf16x2(ov[e + 2] * inv_l, ov[e + 3] * inv_l)),
+                             "r"(pack_bf16x2(ov[e + 4] * inv_l, ov[e + 5] * inv_l)),
+                             "r"(pack_bf16x2(ov[e + 6] * inv_l, ov[e + 7] * inv_l))
+                             : "memory");
             }
+        }
+        fence_async_proxy();               // make the rows visible to the copy engine ...
+        named_bar_sync(1 + t, kBM);        // ... once all 128 threads of this tile have written theirs
+        if (row_in_tile == 0) {
+            tma_store_4d(&tm_o, stage_o, 0, q0 + t * kBM, h, b);
+            tma_store_4d(&tm_o, stage_o + kHalfBytes, 64, q0 + t * kBM, h, b);
+            tma_store_commit_and_wait();
         }
         if (row_ok && p.lse)
             p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] =
@@ -772,10 +848,11 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     const long long blocks = static_cast<long long>(B) * Hq * p.n_qp;
     if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
 
-    CUtensorMap tm_q, tm_k, tm_v;
+    CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if ((rc = encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
     if ((rc = encode_bhsd_map(&tm_k, k, B, Hkv, Skv)) != CLLO_OK) return rc;
     if ((rc = encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
+    if ((rc = encode_bhsd_map(&tm_o, o, B, Hq, Sq)) != CLLO_OK) return rc;
 
     // share of exponentials moved to the FMA pipes, in eighths (tuning knob; default chosen by measurement)
     static const int emu8 = [] {
@@ -803,10 +880,10 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     }
     const unsigned grid = static_cast<unsigned>(blocks);
     switch (emu8) {
-        case 0: prefill_fwd_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
-        case 2: prefill_fwd_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
-        case 3: prefill_fwd_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
-        default: prefill_fwd_kernel<4><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p); break;
+        case 0: prefill_fwd_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
+        case 2: prefill_fwd_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
+        case 3: prefill_fwd_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
+        default: prefill_fwd_kernel<4><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
     }
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
