@@ -396,7 +396,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (j_lo > j_hi - 1) j_lo = j_hi - 1;
     const int n_kv = j_hi - j_lo;  // >= 1; the loops below count local tiles, tile j is global tile j_lo + j
 
-    if (threadIdx.x == 0) {
+    if (warp == 8 && lane == 0) {
         mbar_init(bar_q_full, 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(bar_k_full(s), 1);
@@ -413,6 +413,24 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_init(bar_drain, 1);
         *abort_flag = 0;
         fence_mbar_init();
+        // The first copies start here, before the block has even met at its first barrier: Q, and K and V of the
+        // first kv tile (their stages are fresh, nothing to wait for).  The producer loop below continues at
+        // the second K tile.
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        mbar_arrive_expect_tx(bar_q_full, kTiles * kTileBytes);
+        for (int t = 0; t < kTiles; ++t) {
+            const uint32_t dst = base + kSmemQ + t * kTileBytes;
+            tma_load_4d(dst, &tm_q, bar_q_full, 0, q0 + t * kBM, h, b);
+            tma_load_4d(dst + kHalfBytes, &tm_q, bar_q_full, 64, q0 + t * kBM, h, b);
+        }
+        mbar_arrive_expect_tx(bar_k_full(0), kTileBytes);
+        tma_load_4d(base + kSmemK, &tm_k, bar_k_full(0), 0, j_lo * kBN, kvh, b);
+        tma_load_4d(base + kSmemK + kHalfBytes, &tm_k, bar_k_full(0), 64, j_lo * kBN, kvh, b);
+        mbar_arrive_expect_tx(bar_v_full(0), kTileBytes);
+        tma_load_4d(base + kSmemV, &tm_v, bar_v_full(0), 0, j_lo * kBN, kvh, b);
+        tma_load_4d(base + kSmemV + kHalfBytes, &tm_v, bar_v_full(0), 64, j_lo * kBN, kvh, b);
     }
     if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -430,17 +448,8 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (warp == 8) {
         // ------------------------------- TMA producer -------------------------------
         if (lane == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_k);
-            tma_prefetch_desc(&tm_v);
             tma_prefetch_desc(&tm_o);
-            mbar_arrive_expect_tx(bar_q_full, kTiles * kTileBytes);
-            for (int t = 0; t < kTiles; ++t) {
-                const uint32_t dst = base + kSmemQ + t * kTileBytes;
-                tma_load_4d(dst, &tm_q, bar_q_full, 0, q0 + t * kBM, h, b);
-                tma_load_4d(dst + kHalfBytes, &tm_q, bar_q_full, 64, q0 + t * kBM, h, b);
-            }
-            for (int j = 0; j < n_kv; ++j) {
+            for (int j = 1; j < n_kv; ++j) {  // tile 0 was started before the block's first barrier
                 const int s = j % kKvStages;
                 const uint32_t use = static_cast<uint32_t>(j / kKvStages);
                 mbar_wait(bar_k_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_K_EMPTY, j);
@@ -468,12 +477,15 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     } else if (warp == 9) {
         // -------------------------------- MMA issuer --------------------------------
-        // Lane 0 issues every tcgen05.mma.  The tensor pipe runs only a couple of instructions behind the issuing
-        // thread, and whatever that thread does between two MMAs (an mbarrier look-up costs well over a hundred
-        // cycles while the pipe saturates the shared-memory port, a commit about as much) is time the pipe idles.
+        // Lane 0 issues every tcgen05.mma.  Measured on this part: a stream of these MMAs runs at 64 cycles each and
+        // absorbs a couple of hundred cycles of plain arithmetic in the issuing thread, but NOT its memory-pipe
+        // instructions -- those are carried out in order behind the queued MMAs, so a look at an mbarrier whose
+        // result is needed at once (about 150-190 cycles round trip while the tensor pipe saturates the
+        // shared-memory port), a named barrier or a commit each leave the tensor pipe idle for about that long.
         // So the work is issued in runs of sixteen MMAs -- the next S for region C (the other tile will be waiting for
-        // it before anybody waits for P V), then O_t += P_t V of the tile that has just finished its softmax -- with
-        // ONE look at the barriers before a run (the whole warp looks at once, one barrier per lane).
+        // it before anybody waits for P V), then O_t += P_t V of the tile that has just finished its softmax -- and
+        // the look at the next run's barriers (the whole warp looks at once, one barrier per lane) is issued inside
+        // the P V run with its result read only after the run's last MMA.
         // low descriptor words of the operand tiles (per k step only a constant is added: the tiles are 1024-byte
         // aligned and no sum leaves the 14-bit address field)
         const uint32_t hi = smem_desc_hi(1024);
