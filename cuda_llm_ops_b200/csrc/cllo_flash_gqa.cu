@@ -5,6 +5,7 @@
 #include "gqa_exchange.cuh"
 #include "gqa_backward.cuh"
 #include "rope.cuh"
+#include "sgqa_prefill.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -219,6 +220,13 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
     if (window_size <= 0 || !sink_value) return CLLO_E_BAD_ARG;
     return prefill::launch(q, k, v, scale, 1, window_size, sink_value, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
+}
+
+int cllo_sgqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, const int* sparse_kv_indices,
+                               int num_sparse_kv, float scale, int causal, void* o, float* lse, int B, int Sq, int Skv,
+                               int Hq, int Hkv, int D, void* stream) {
+    return sgqa::launch(q, k, v, sparse_kv_indices, num_sparse_kv, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D,
+                        static_cast<cudaStream_t>(stream));
 }
 
 // Decode for callers that may not allocate device memory: the partials go to the fixed array above.

@@ -324,6 +324,94 @@ def launch_flash_swa_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None
     return out_b, lse_b
 
 
+def launch_flash_sgqa_forward_bf16_kernel(q, k, v, sparse_kv_indices, num_sparse_kv, scale=None, out=None, lse=None,
+                                          causal=True, block_sparse_sub=None, num_warps=None, num_stages=None):
+    """Mirror of upstream's sparse-index GQA launcher (src/python/Triton/SparseGQA/flash_sgqa_kernel.py:202-396).
+
+    ``sparse_kv_indices`` (int32 ``[batch, num_kv_heads, seqlen_q, num_sparse_kv]``) lists, per kv head and query token,
+    the kv tokens that token attends to; entries outside ``[0, seqlen_kv)`` (upstream pads with -1) and, when
+    ``causal``, entries above the query position are ignored.  Same ranks, layouts, checks and return value
+    ``(out, lse)`` as upstream; its Triton tuning keywords are validated as upstream does and otherwise ignored.
+    """
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("Flash SGQA forward expects bf16 inputs")
+    if sparse_kv_indices.dtype != torch.int32:
+        raise ValueError("sparse_kv_indices must be int32")
+    if sparse_kv_indices.dim() != 4:
+        raise ValueError("sparse_kv_indices must be 4D [batch, num_kv_heads, seqlen_q, num_sparse_kv]")
+    if not isinstance(num_sparse_kv, int):
+        raise ValueError("num_sparse_kv must be an int")
+    if num_sparse_kv < 1:
+        raise ValueError("num_sparse_kv must be >= 1")
+    if block_sparse_sub is not None and (not isinstance(block_sparse_sub, int) or block_sparse_sub < 1):
+        raise ValueError("block_sparse_sub must be None or an int >= 1")
+    if num_warps is not None and (not isinstance(num_warps, int) or num_warps < 1):
+        raise ValueError("num_warps must be None or an int >= 1")
+    if num_stages is not None and (not isinstance(num_stages, int) or num_stages < 1):
+        raise ValueError("num_stages must be None or an int >= 1")
+    if q.dim() not in (3, 4):
+        raise ValueError("Q must be 3D or 4D")
+    if k.dim() != q.dim() or v.dim() != q.dim():
+        raise ValueError("Q, K, and V must have matching ranks")
+    squeeze = q.dim() == 3
+    qb, kb, vb = (t.contiguous().unsqueeze(0) if squeeze else t.contiguous() for t in (q, k, v))
+    batch, q_heads, seqlen_q, head_dim_qk = qb.shape
+    _, num_kv_heads, seqlen_kv, k_head_dim = kb.shape
+    _, v_heads, v_seqlen, head_dim_v = vb.shape
+    if seqlen_kv != v_seqlen:
+        raise ValueError("K and V must share sequence length")
+    if k_head_dim != head_dim_qk:
+        raise ValueError("Q and K must share head_dim_qk")
+    if v_heads != num_kv_heads:
+        raise ValueError("K and V must share number of KV heads")
+    if q_heads % num_kv_heads != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    if tuple(sparse_kv_indices.shape) != (batch, num_kv_heads, seqlen_q, num_sparse_kv):
+        raise ValueError("sparse_kv_indices must have shape "
+                         f"[batch, num_kv_heads, seqlen_q, {num_sparse_kv}]")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t)
+    if sparse_kv_indices.device != qb.device:
+        raise ValueError("sparse_kv_indices must be on the same device as Q")
+    if head_dim_qk != HEAD_DIM or head_dim_v != HEAD_DIM:
+        raise ValueError("this build supports head_dim == 128 only")
+    if q_heads // num_kv_heads > 16:
+        raise ValueError("this build supports at most 16 query heads per KV head")
+    idx = sparse_kv_indices.contiguous()
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim_qk)
+    if out is None:
+        out_b = torch.empty((batch, q_heads, seqlen_q, head_dim_v), device=qb.device, dtype=qb.dtype)
+    else:
+        if out.dim() != q.dim():
+            raise ValueError("Output must be 3D when Q is 3D" if squeeze else "Output must be 4D when Q is 4D")
+        if not out.is_contiguous():
+            raise ValueError("Output must be contiguous when provided")
+        out_b = out.unsqueeze(0) if squeeze else out
+    if tuple(out_b.shape) != (batch, q_heads, seqlen_q, head_dim_v):
+        raise ValueError("Output must have shape [batch, q_heads, seqlen_q, head_dim_v]")
+    if lse is None:
+        lse_b = torch.empty((batch, q_heads, seqlen_q), device=qb.device, dtype=torch.float32)
+    else:
+        if lse.dim() != q.dim() - 1:
+            raise ValueError("LSE must be 2D when Q is 3D" if squeeze else "LSE must be 3D when Q is 4D")
+        if not lse.is_contiguous():
+            raise ValueError("LSE must be contiguous when provided")
+        lse_b = lse.unsqueeze(0) if squeeze else lse
+    if tuple(lse_b.shape) != (batch, q_heads, seqlen_q) or lse_b.dtype != torch.float32:
+        raise ValueError("LSE must have shape [batch, q_heads, seqlen_q]")
+    if seqlen_q > 0:
+        with torch.cuda.device(qb.device):
+            rc = _lib.load().cllo_sgqa_prefill_fwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), idx.data_ptr(),
+                                                        num_sparse_kv, float(scale), 1 if causal else 0,
+                                                        out_b.data_ptr(), lse_b.data_ptr(), batch, seqlen_q, seqlen_kv,
+                                                        q_heads, num_kv_heads, head_dim_qk, _stream_ptr())
+        _lib.check(rc, "cllo_sgqa_prefill_fwd_bf16")
+    if squeeze:
+        return out_b.squeeze(0), lse_b.squeeze(0)
+    return out_b, lse_b
+
+
 def launch_flash_gqa_backward_bf16_kernel(q, k, v, o, lse, grad_o, scale=None, causal=True, **_tuning):
     """Mirror of upstream's backward launcher (src/python/Triton/flash_gqa_backward_kernel.py:312-478).
 

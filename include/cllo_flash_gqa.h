@@ -165,6 +165,20 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
 /*
+ * Sparse-index GQA forward: every query token attends to its own list of kv tokens, shared by the query heads
+ * of a group.  Stands in for flash_sgqa_forward_bf16_kernel + launch_flash_sgqa_forward_bf16_kernel
+ * (src/python/Triton/SparseGQA/flash_sgqa_kernel.py:15-138, :202-396).
+ *   q,o [B,Hq,Sq,D]   k,v [B,Hkv,Skv,D]   lse [B,Hq,Sq] fp32 (nullable)
+ *   sparse_kv_indices int32 [B,Hkv,Sq,num_sparse_kv] on the device
+ * An entry counts when 0 <= index < Skv and, with causal != 0, index <= the query position; every other entry
+ * (upstream pads with -1) is ignored, repeated entries count as often as they appear, a row whose list holds no
+ * valid entry gives zeros and lse = -inf.  D = 128 and Hq / Hkv <= 16.
+ */
+int cllo_sgqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, const int* sparse_kv_indices,
+                               int num_sparse_kv, float scale, int causal, void* o, float* lse,
+                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
+/*
  * GQA attention backward: grad_q, grad_k, grad_v from grad_o, given the forward's inputs, output and lse.
  * Stands in for flash_gqa_backward_bf16_kernel + rowwise_dot_o_grad_o_kernel +
  * launch_flash_gqa_backward_bf16_kernel (src/python/Triton/flash_gqa_backward_kernel.py:159-310, :16-48,

@@ -356,6 +356,83 @@ int cllo_oracle_swa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uin
 }
 
 /*
+ * Sparse-index GQA forward: restates flash_sgqa_forward_reference of
+ * examples/python/Triton/test_flash_sgqa_kernel.py:102-216.  Per (batch, kv head, query token) a list of kv token
+ * indices, shared by the query heads of the group (:185-189); an entry counts when 0 <= index < Skv and, if causal,
+ * index <= query position (:191-193); fp32 scores * scale with the other entries at -inf (:199-200); row max,
+ * exp, the masked entries forced to 0 (:202-204); probs = exp / denom, zero when denom = 0 (:205-206);
+ * out = probs @ V_gathered in fp32, rounded to bf16 (:208,217); lse = log(denom) + max, -inf when denom = 0
+ * (:209-213).  Repeated indices count as often as they are listed.
+ */
+int cllo_oracle_sgqa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const int32_t* sparse_idx,
+                                  int num_sparse, float scale, int causal, uint16_t* o, float* lse,
+                                  int B, int Sq, int Skv, int Hq, int Hkv, int D) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || num_sparse <= 0 || !sparse_idx) return -1;
+    if (Hq % Hkv != 0) return -1;
+    const int G = Hq / Hkv;
+    const int64_t total = (int64_t)B * Hq * Sq;
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* sc = (float*)malloc(sizeof(float) * (size_t)num_sparse);
+        float* oacc = (float*)malloc(sizeof(float) * (size_t)D);
+        float* qf = (float*)malloc(sizeof(float) * (size_t)D);
+        if (!sc || !oacc || !qf) {
+#pragma omp atomic write
+            failed = 1;
+        } else {
+#pragma omp for schedule(dynamic, 16)
+            for (int64_t idx = 0; idx < total; ++idx) {
+                const int64_t b = idx / ((int64_t)Hq * Sq);
+                const int64_t h = (idx / Sq) % Hq;
+                const int64_t i = idx % Sq;
+                const int64_t kvh = h / G;
+                const uint16_t* qrow = q + ((b * Hq + h) * Sq + i) * D;
+                const uint16_t* kb = k + (b * Hkv + kvh) * (int64_t)Skv * D;
+                const uint16_t* vb = v + (b * Hkv + kvh) * (int64_t)Skv * D;
+                const int32_t* list = sparse_idx + ((b * Hkv + kvh) * Sq + i) * (int64_t)num_sparse;
+                for (int d = 0; d < D; ++d) qf[d] = bf16_to_f32(qrow[d]);
+                for (int d = 0; d < D; ++d) oacc[d] = 0.f;
+                float rmax = -INFINITY;
+                for (int e = 0; e < num_sparse; ++e) {
+                    const int64_t j = list[e];
+                    const int ok = j >= 0 && j < Skv && (!causal || j <= i);
+                    if (!ok) {
+                        sc[e] = -INFINITY;
+                        continue;
+                    }
+                    float acc = 0.f;
+                    const uint16_t* kr = kb + j * D;
+                    for (int d = 0; d < D; ++d) acc += qf[d] * bf16_to_f32(kr[d]);
+                    sc[e] = acc * scale;
+                    rmax = fmaxf(rmax, sc[e]);
+                }
+                float denom = 0.f;
+                for (int e = 0; e < num_sparse; ++e) {
+                    sc[e] = sc[e] == -INFINITY ? 0.f : expf(sc[e] - rmax);
+                    denom += sc[e];
+                }
+                if (denom > 0.f) {
+                    for (int e = 0; e < num_sparse; ++e) {
+                        if (sc[e] == 0.f) continue;
+                        const float p = sc[e] / denom;
+                        const uint16_t* vr = vb + (int64_t)list[e] * D;
+                        for (int d = 0; d < D; ++d) oacc[d] += p * bf16_to_f32(vr[d]);
+                    }
+                }
+                if (o)
+                    for (int d = 0; d < D; ++d) o[((b * Hq + h) * Sq + i) * D + d] = f32_to_bf16(oacc[d]);
+                if (lse) lse[(b * Hq + h) * Sq + i] = denom > 0.f ? logf(denom) + rmax : -INFINITY;
+            }
+        }
+        free(sc);
+        free(oacc);
+        free(qf);
+    }
+    return failed ? -2 : 0;
+}
+
+/*
  * GQA attention backward, layout q,o,grad_o,grad_q [B,Hq,Sq,D]; k,v,grad_k,grad_v [B,Hkv,Skv,D] (bf16).
  *
  * Follows examples/python/Triton/test_flash_gqa_kernel.py:97-173: probabilities are recomputed from

@@ -11,6 +11,9 @@ It imports, unmodified,
     (full softmax, causal, returns the log-sum-exp),
   * ``flash_swa_forward_reference``  examples/python/Triton/test_flash_swa_kernel.py:28-118
     (sliding window + sink term),
+  * ``flash_sgqa_forward_reference`` examples/python/Triton/test_flash_sgqa_kernel.py:102-216
+    (sparse-index GQA; the list length is a module constant there, 512, which the script sets to the small
+    length of its cases before calling the function),
 feeds them small seeded N(0,1) bf16 tensors and stores inputs and outputs (bf16 as uint16 bit
 patterns) in ``gqa_golden.npz``.  The tests compare both the C oracle and the CUDA kernels with
 these files, so the oracle is pinned to upstream's own code rather than to itself.
@@ -121,6 +124,39 @@ def main():
         out[name + "/lse"] = lse.numpy().astype(np.float32)
         out[name + "/sink"] = sink.numpy().astype(np.float32)
         out[name + "/window"] = np.array(window)
+        meta.append(name)
+
+    # --- sparse-index GQA forward (upstream flash_sgqa_forward_reference, test_flash_sgqa_kernel.py:102-216) ---
+    import test_flash_sgqa_kernel as sg  # noqa: E402
+    sgqa_cases = [
+        # name,          Hq, Hkv, Sq, Skv, n_sparse, causal
+        ("sgqa_g4_n40",   4,  1,  96,  96,  40, True),    # list length not a multiple of 16; early rows are padded with -1
+        ("sgqa_g2_n16",   4,  2,  48,  80,  16, False),   # two kv heads with lists of their own; entries above q allowed
+    ]
+    for i, (name, Hq, Hkv, Sq, Skv, n_sparse, causal) in enumerate(sgqa_cases):
+        g = torch.Generator().manual_seed(6000 + i)
+        q = torch.randn(Hq, Sq, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, Skv, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, Skv, 128, generator=g).to(torch.bfloat16)
+        idx = torch.full((1, Hkv, Sq, n_sparse), -1, dtype=torch.int32)
+        for h in range(Hkv):
+            for qi in range(Sq):
+                hi = min(qi, Skv - 1) if causal else Skv - 1
+                take = min(n_sparse, hi + 1)
+                perm = torch.randperm(hi + 1, generator=g)[:take].to(torch.int32)
+                idx[0, h, qi, :take] = perm
+        # a few hostile entries: out of range, above the query position, repeated, and one empty list
+        idx[0, 0, 5, 0] = Skv + 7
+        idx[0, 0, 6, 1] = idx[0, 0, 6, 0]
+        idx[0, 0, 7, :] = -1
+        if causal:
+            idx[0, 0, 9, 2] = 50
+        sg.NUM_SPARSE_KV = n_sparse
+        o, lse = sg.flash_sgqa_forward_reference(q, k, v, idx, return_lse=True, causal=causal)
+        out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
+        out[name + "/idx"] = idx.numpy().astype(np.int32)
+        out[name + "/causal"] = np.array(1 if causal else 0)
         meta.append(name)
 
     out["cases"] = np.array(meta)

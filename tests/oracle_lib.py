@@ -142,6 +142,23 @@ def swa_prefill(q, k, v, scale, window, sink):
     return o, lse
 
 
+def sgqa_prefill(q, k, v, sparse_idx, scale, causal=True):
+    """Sparse-index GQA forward: q [B,Hq,Sq,D], k,v [B,Hkv,Skv,D] uint16, sparse_idx int32 [B,Hkv,Sq,n] -> (o, lse)."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v))
+    sparse_idx = np.ascontiguousarray(sparse_idx, dtype=np.int32)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    assert sparse_idx.shape[:3] == (B, Hkv, Sq), sparse_idx.shape
+    o = np.zeros((B, Hq, Sq, D), dtype=np.uint16)
+    lse = np.zeros((B, Hq, Sq), dtype=np.float32)
+    rc = lib().cllo_oracle_sgqa_prefill_bf16(
+        _ptr(q, ctypes.c_uint16), _ptr(k, ctypes.c_uint16), _ptr(v, ctypes.c_uint16), _ptr(sparse_idx, ctypes.c_int32),
+        int(sparse_idx.shape[3]), ctypes.c_float(scale), 1 if causal else 0, _ptr(o, ctypes.c_uint16),
+        _ptr(lse, ctypes.c_float), B, Sq, Skv, Hq, Hkv, D)
+    assert rc == 0, rc
+    return o, lse
+
+
 def backward(q, k, v, o, grad_o, scale, causal):
     """q,o,grad_o [B,Hq,Sq,D], k,v [B,Hkv,Skv,D] uint16 -> (grad_q, grad_k, grad_v) bits."""
     q, k, v, o, grad_o = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v, o, grad_o))

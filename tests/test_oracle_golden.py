@@ -59,6 +59,32 @@ def test_swa_oracle_matches_upstream_torch_oracle(golden, name):
     assert np.allclose(got_lse[0], golden[name + "/lse"], atol=2e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["sgqa_g4_n40", "sgqa_g2_n16"])
+def test_sgqa_oracle_matches_upstream_torch_oracle(golden, name):
+    q, k, v, o = (golden[name + "/" + t][None] for t in ("q", "k", "v", "o"))
+    got_o, got_lse = ol.sgqa_prefill(q, k, v, golden[name + "/idx"], SCALE, bool(golden[name + "/causal"]))
+    mx, mean, rel = ol.errors(got_o, o)
+    assert mx <= 4e-3 and mean <= 2e-4 and rel <= 4e-3, (mx, mean, rel)
+    want_lse = golden[name + "/lse"]
+    finite = np.isfinite(want_lse)
+    assert np.array_equal(np.isfinite(got_lse[0]), finite)            # the empty list gives -inf in both
+    assert np.allclose(got_lse[0][finite], want_lse[finite], atol=2e-5, rtol=1e-5)
+    assert not finite.all()
+
+
+def test_sgqa_oracle_with_the_full_causal_list_is_causal_attention():
+    B, Hq, Hkv, S = 1, 4, 2, 40
+    q = ol.randn_bf16((B, Hq, S, 128), 41)
+    k = ol.randn_bf16((B, Hkv, S, 128), 42)
+    v = ol.randn_bf16((B, Hkv, S, 128), 43)
+    idx = np.broadcast_to(np.arange(S, dtype=np.int32)[::-1], (B, Hkv, S, S)).copy()   # every token, any order
+    o_sparse, lse_sparse = ol.sgqa_prefill(q, k, v, idx, SCALE, causal=True)
+    o_dense, lse_dense = ol.prefill(q, k, v, SCALE, True)
+    mx, mean, rel = ol.errors(o_sparse, o_dense)
+    assert mx <= 4e-3 and mean <= 2e-4, (mx, mean, rel)
+    assert np.allclose(lse_sparse, lse_dense, atol=2e-5, rtol=1e-5)
+
+
 def test_swa_oracle_with_a_window_wider_than_the_sequence_is_causal_attention_plus_sink():
     q = ol.randn_bf16((1, 2, 50, 128), 14)
     k = ol.randn_bf16((1, 1, 50, 128), 15)
