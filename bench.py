@@ -10,6 +10,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
     prefill_causal  prefill forward, causal, B=8 in total (strong scaling), S=16384, Hq=64, Hkv=8; batch-sharded
     rope            rotary position embedding, upstream's shape
+    sgqa            sparse-index GQA forward, upstream's shape (S=32768, 16 query heads on one kv head, lists of 512)
     backward        GQA attention backward (dQ, dK, dV), causal, upstream's shape
     swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
 
@@ -221,6 +222,34 @@ def run_ours(args, rank, world, local_rank):
                   "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
                   "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
         host_in = [x]
+    elif wl == "sgqa":
+        # upstream's sparse-index GQA benchmark shape (README: 3690 us / 37.2 TFLOPS on an RTX 5080 Laptop).  Lists as
+        # in upstream's test: the 16 most recent tokens, then uniformly drawn earlier ones, padded with -1 while the
+        # prefix is shorter than the list (drawn with replacement here; upstream draws without).
+        B, S, Hq, Hkv, n_sparse = 1, 32768, 16, 1, 512
+        q, k, v = randn_bf16((B, Hq, S, 128)), randn_bf16((B, Hkv, S, 128)), randn_bf16((B, Hkv, S, 128))
+        pos = torch.arange(S, device=dev, dtype=torch.int32).view(1, 1, S, 1)
+        gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+        idx = (torch.rand((B, Hkv, S, n_sparse), generator=gen, device=dev) * (pos - 15).clamp(min=1)).to(torch.int32)
+        slot = torch.arange(n_sparse, device=dev, dtype=torch.int32).view(1, 1, 1, n_sparse)
+        idx = torch.where(slot < 16, pos - slot, idx)                     # the recent window
+        idx = torch.where((slot <= pos) & (idx >= 0), idx, torch.full_like(idx, -1)).contiguous()
+        out = torch.empty_like(q)
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.launch_flash_sgqa_forward_bf16_kernel(q, k, v, idx, n_sparse, out=out, lse=lse)  # noqa: E731
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        # upstream's FLOP convention: 4 * heads * tokens * list length * head_dim (test_flash_sgqa_kernel.py)
+        units_per_rank = 4.0 * B * Hq * S * n_sparse * 128
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "sgqa_prefill_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "sgqa: sparse-index GQA forward, causal, B=1, S=32768, Hq=16, Hkv=1, D=128, "
+                              "512 list entries per token (16 recent + uniform earlier ones)",
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [q, k, v, idx]
     elif wl == "backward":
         # upstream's backward benchmark shape (README: 3100 us / 55 TFLOPS on an RTX 5080 Laptop), causal
         B, S, Hq, Hkv = 1, 4096, 16, 1
@@ -302,7 +331,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl in ("prefill_nc", "swa", "backward", "rope"):
+    if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -398,7 +427,9 @@ def run_ours(args, rank, world, local_rank):
                 "kernel": "rope_bf16_kernel" if wl == "rope" else "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
                           "which also holds the merge pass and launch gaps" if bound == "hbm"
                           else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
-                                else "prefill_fwd_kernel"),
+                                else ("sgqa_fwd_kernel (bound by gathering 512 B per list entry out of L2, mma.sync "
+                                      "products; the tensor peak is quoted for scale only)" if wl == "sgqa"
+                                      else "prefill_fwd_kernel")),
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
@@ -509,7 +540,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

@@ -22,17 +22,19 @@
 #include "common.cuh"
 #include "host_util.cuh"
 
+#include <cstdlib>
+
 namespace cllo {
 namespace sgqa {
 
 constexpr int kD = 128;
 constexpr int kRows = 16;        // query heads per mma tile (G <= 16, zero padded)
 constexpr int kChunk = 16;       // list entries per gather
-constexpr int kWarps = 8;
-constexpr int kBufs = 3;         // ring of gather buffers per warp: two gathers in flight
+constexpr int kDefaultWarps = 12;
+constexpr int kDefaultBufs = 2;  // ring of gather buffers per warp: one gather in flight behind the one in use
 constexpr int kHalfBytes = kChunk * 128;        // [16 rows][64 dims] bf16
 constexpr int kBufBytes = 4 * kHalfBytes;       // K (2 halves) + V (2 halves) = 8 KB
-constexpr int kSmemBytes = kWarps * kBufs * kBufBytes + 1024;
+constexpr int smem_bytes(int warps, int bufs) { return warps * bufs * kBufBytes + 1024; }
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -57,6 +59,7 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
+template <int kWarps, int kBufs>
 __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -127,30 +130,43 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
         for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-        uint32_t mask_cur = gather(0), mask_nxt = gather(1);
+        // kBufs = 3: two gathers run ahead of the one being consumed; kBufs = 2: one (the gather issued in iteration c
+        // is then c + 1, and the mask pipeline is one step shorter)
+        uint32_t mask_cur = gather(0), mask_nxt = kBufs == 2 ? 0u : gather(1);
 #pragma unroll 1
         for (int c = 0; c < n_chunks; ++c) {
-            const uint32_t mask_new = gather(c + 2);
-            cp_async_wait<2>();
+            const uint32_t mask_new = gather(kBufs == 2 ? c + 1 : c + 2);
+            cp_async_wait<kBufs == 2 ? 1 : 2>();
             __syncwarp();
             if (mask_cur != 0) {
                 const uint32_t kb = ring + (c % kBufs) * kBufBytes;
                 const uint32_t vb = kb + 2 * kHalfBytes;
                 // ---- S = Q K^T  (16 heads x 16 entries) ----
-                float s[2][4];
+                // (two accumulators per 8 entries, summed at the end: four independent chains of four MMAs instead
+                // of two chains of eight -- a warp has few neighbours to hide the MMA latency behind)
+                float s[2][4], s2[2][4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-                    const uint32_t row_off = static_cast<uint32_t>(nt * 8 + (lane & 7)) * 128u;
+                    s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+                }
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const uint32_t row_off = static_cast<uint32_t>(nt * 8 + (lane & 7)) * 128u;
                         const uint32_t chunk = static_cast<uint32_t>((kk & 1) * 4 + (lane >> 3));
                         const uint32_t addr = kb + (kk >> 1) * kHalfBytes + row_off + ((chunk ^ (lane & 7)) << 4);
                         uint32_t b0, b1, b2, b3;
                         ldmatrix_x4(addr, b0, b1, b2, b3);
                         mma_bf16_16816(s[nt], qf[2 * kk], b0, b1);
-                        mma_bf16_16816(s[nt], qf[2 * kk + 1], b2, b3);
+                        mma_bf16_16816(s2[nt], qf[2 * kk + 1], b2, b3);
                     }
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
                 }
                 // ---- online softmax ----
                 float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -210,7 +226,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
                 }
             }
             __syncwarp();  // every lane is done with this buffer before gather(c + 3) overwrites it
-            mask_cur = mask_nxt;
+            mask_cur = kBufs == 2 ? mask_new : mask_nxt;
             mask_nxt = mask_new;
         }
         cp_async_wait<0>();
@@ -282,14 +298,28 @@ static int launch(const void* q, const void* k, const void* v, const int* idx, i
     p.num_sparse = num_sparse;
     p.n_tokens = static_cast<long long>(B) * Hkv * Sq;
 
-    if (!di->sgqa_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(sgqa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        di->sgqa_attr_set = true;
+    // warps per block x ring depth (tuning knob; the default was chosen by measurement)
+    static const int cfg = [] {
+        const char* e = std::getenv("CLLO_SGQA_CFG");
+        const int v = e ? std::atoi(e) : 0;
+        return (v == 83 || v == 122 || v == 142 || v == 102) ? v : kDefaultWarps * 10 + kDefaultBufs;
+    }();
+    auto run = [&](auto kernel, int warps, int bufs) -> int {
+        const int smem = smem_bytes(warps, bufs);
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        const long long want = (p.n_tokens + warps - 1) / warps;
+        const long long cap = static_cast<long long>(di->sm_count) * 8;  // a few rounds per SM: lists differ in length
+        const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+        kernel<<<grid, warps * 32, smem, stream>>>(p);
+        return CLLO_OK;
+    };
+    switch (cfg) {
+        case 142: rc = run(sgqa_fwd_kernel<14, 2>, 14, 2); break;
+        case 102: rc = run(sgqa_fwd_kernel<10, 2>, 10, 2); break;
+        case 83: rc = run(sgqa_fwd_kernel<8, 3>, 8, 3); break;
+        default: rc = run(sgqa_fwd_kernel<12, 2>, 12, 2); break;
     }
-    const long long want = (p.n_tokens + kWarps - 1) / kWarps;
-    const long long cap = static_cast<long long>(di->sm_count) * 8;  // a few rounds per SM: tokens differ in list length
-    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-    sgqa_fwd_kernel<<<grid, kWarps * 32, kSmemBytes, stream>>>(p);
+    if (rc != CLLO_OK) return rc;
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }
