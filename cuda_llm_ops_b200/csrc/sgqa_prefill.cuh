@@ -68,6 +68,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
     const uint32_t ring = base + warp * (kBufs * kBufBytes);
     const int n_chunks = (p.num_sparse + kChunk - 1) / kChunk;
     const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+    // gather, per lane: 16-byte piece (lane & 15) of rows (lane >> 4) + 2i; destination offset of row (lane >> 4)
+    const uint32_t src_lane = static_cast<uint32_t>((lane & 15) * 16);
+    const uint32_t dst_lane = static_cast<uint32_t>(((lane & 15) >> 3) * kHalfBytes + (lane >> 4) * 128);
+    const uint32_t xor_lane = static_cast<uint32_t>((lane & 7) ^ (lane >> 4));  // piece index XOR (row & 1)
 
 #pragma unroll 1
     for (long long tok = static_cast<long long>(blockIdx.x) * kWarps + warp; tok < p.n_tokens; tok += stride) {
@@ -78,6 +82,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
         const __nv_bfloat16* kbase = p.k + (static_cast<long long>(b) * p.Hkv + kvh) * p.Skv * kD;
         const __nv_bfloat16* vbase = p.v + (static_cast<long long>(b) * p.Hkv + kvh) * p.Skv * kD;
         const int* list = p.idx + tok * p.num_sparse;
+        const long long v_minus_k = reinterpret_cast<const char*>(vbase) - reinterpret_cast<const char*>(kbase);
 
         // Q fragments (A operand: rows = query heads of the group, zero padded to 16)
         uint32_t qf[8][4];
@@ -106,18 +111,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
                 e = ok ? e : -1;
                 mask = __ballot_sync(0xffffffffu, ok) & 0xffffu;
                 if (mask != 0) {
-                    const uint32_t buf = ring + (c % kBufs) * kBufBytes;
-                    const int c16 = lane & 15;  // 16-byte piece of the 256-byte row
-                    const uint32_t piece = static_cast<uint32_t>((c16 >> 3) * kHalfBytes);
+                    const uint32_t buf = ring + (c % kBufs) * kBufBytes + dst_lane;
+                    const char* ksrc = reinterpret_cast<const char*>(kbase) + src_lane;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const int row = 2 * i + (lane >> 4);
-                        const int src_row = __shfl_sync(0xffffffffu, e, row);
-                        const uint32_t dst = buf + piece + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
-                        const long long off = static_cast<long long>(src_row < 0 ? 0 : src_row) * kD + c16 * 8;
+                        const int src_row = __shfl_sync(0xffffffffu, e, 2 * i + (lane >> 4));
+                        // row 2i + (lane >> 4): 256 bytes per step of i, the piece index XOR-ed with row & 7
+                        const uint32_t dst = buf + i * 256 + ((xor_lane ^ static_cast<uint32_t>((2 * i) & 7)) << 4);
+                        const char* src = ksrc + static_cast<long long>(src_row < 0 ? 0 : src_row) * (kD * 2);
                         const uint32_t bytes = src_row < 0 ? 0u : 16u;  // 0: the 16 bytes are zero-filled
-                        cp_async_16(dst, kbase + off, bytes);
-                        cp_async_16(dst + 2 * kHalfBytes, vbase + off, bytes);
+                        cp_async_16(dst, src, bytes);
+                        cp_async_16(dst + 2 * kHalfBytes, src + v_minus_k, bytes);
                     }
                 }
             }
@@ -170,16 +174,26 @@ __global__ void __launch_bounds__(kWarps * 32, 1) sgqa_fwd_kernel(const Params p
                 }
                 // ---- online softmax ----
                 float mx0 = -INFINITY, mx1 = -INFINITY;
+                if (mask_cur == 0xffffu) {  // the usual case: all 16 entries count
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const int col = nt * 8 + tig * 2;
-                    const bool ok0 = (mask_cur >> col) & 1u, ok1 = (mask_cur >> (col + 1)) & 1u;
-                    s[nt][0] = ok0 ? s[nt][0] * p.scale_log2 : -INFINITY;
-                    s[nt][2] = ok0 ? s[nt][2] * p.scale_log2 : -INFINITY;
-                    s[nt][1] = ok1 ? s[nt][1] * p.scale_log2 : -INFINITY;
-                    s[nt][3] = ok1 ? s[nt][3] * p.scale_log2 : -INFINITY;
-                    mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-                    mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+                    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
+                        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int col = nt * 8 + tig * 2;
+                        const bool ok0 = (mask_cur >> col) & 1u, ok1 = (mask_cur >> (col + 1)) & 1u;
+                        s[nt][0] = ok0 ? s[nt][0] * p.scale_log2 : -INFINITY;
+                        s[nt][2] = ok0 ? s[nt][2] * p.scale_log2 : -INFINITY;
+                        s[nt][1] = ok1 ? s[nt][1] * p.scale_log2 : -INFINITY;
+                        s[nt][3] = ok1 ? s[nt][3] * p.scale_log2 : -INFINITY;
+                        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+                    }
                 }
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
