@@ -10,6 +10,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
     prefill_causal  prefill forward, causal, B=8 in total (strong scaling), S=16384, Hq=64, Hkv=8; batch-sharded
     rope            rotary position embedding, upstream's shape
+    mla             MLA-shaped forward (head_dim_qk 192, head_dim_v 128), causal, upstream's shape
     sgqa            sparse-index GQA forward, upstream's shape (S=32768, 16 query heads on one kv head, lists of 512)
     backward        GQA attention backward (dQ, dK, dV), causal, upstream's shape
     swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
@@ -222,6 +223,25 @@ def run_ours(args, rank, world, local_rank):
                   "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
                   "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
         host_in = [x]
+    elif wl == "mla":
+        # upstream's MLA forward benchmark shape (README: 1440 us / 59.65 TFLOPS on an RTX 5080 Laptop), causal
+        B, S, Hq, Hkv = 1, 4096, 16, 16
+        q, k, v = randn_bf16((B, Hq, S, 192)), randn_bf16((B, Hkv, S, 192)), randn_bf16((B, Hkv, S, 128))
+        out = torch.empty((B, Hq, S, 128), dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.launch_flash_mla_forward_bf16_kernel(q, k, v, out=out, lse=lse, causal=True)  # noqa: E731
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        # upstream's FLOP convention: 2 * Sq * Skv * (head_dim_qk + head_dim_v) / 2 per head (test_flash_mla_kernel.py:282-302)
+        units_per_rank = float(B * Hq) * (2 * S * S * (192 + 128) // 2)
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "mla_prefill_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "mla: MLA-shaped forward, causal, B=1, S=4096, Hq=16, Hkv=16, head_dim_qk=192, head_dim_v=128",
+                  "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [q, k, v]
     elif wl == "sgqa":
         # upstream's sparse-index GQA benchmark shape (README: 3690 us / 37.2 TFLOPS on an RTX 5080 Laptop).  Lists as
         # in upstream's test: the 16 most recent tokens, then uniformly drawn earlier ones, padded with -1 while the
@@ -331,7 +351,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa"):
+    if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa", "mla"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -429,7 +449,7 @@ def run_ours(args, rank, world, local_rank):
                           else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
                                 else ("sgqa_fwd_kernel (bound by gathering 512 B per list entry out of L2, mma.sync "
                                       "products; the tensor peak is quoted for scale only)" if wl == "sgqa"
-                                      else "prefill_fwd_kernel")),
+                                      else ("mla_fwd_kernel" if wl == "mla" else "prefill_fwd_kernel"))),
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
@@ -540,7 +560,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

@@ -17,6 +17,7 @@ from .flash_gqa import (  # noqa: F401
     launch_decode_flash_gqa_bf16_kernel,
     launch_flash_gqa_backward_bf16_kernel,
     launch_flash_gqa_forward_bf16_kernel,
+    launch_flash_mla_forward_bf16_kernel,
     launch_flash_sgqa_forward_bf16_kernel,
     launch_flash_swa_backward_bf16_kernel,
     launch_flash_swa_forward_bf16_kernel,

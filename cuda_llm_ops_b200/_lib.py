@@ -38,6 +38,7 @@ _SIGNATURES = {
     "cllo_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _f, _vp]),
     "cllo_swa_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_swa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "cllo_mla_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_sgqa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _f, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_decode_bf16_noalloc": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_decode_bf16_compat": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i]),

@@ -6,6 +6,7 @@
 #include "gqa_backward.cuh"
 #include "rope.cuh"
 #include "sgqa_prefill.cuh"
+#include "mla_prefill.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -220,6 +221,11 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
     if (window_size <= 0 || !sink_value) return CLLO_E_BAD_ARG;
     return prefill::launch(q, k, v, scale, 1, window_size, sink_value, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
+}
+
+int cllo_mla_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse,
+                              int B, int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, void* stream) {
+    return mla::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, Dqk, Dv, static_cast<cudaStream_t>(stream));
 }
 
 int cllo_sgqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, const int* sparse_kv_indices,

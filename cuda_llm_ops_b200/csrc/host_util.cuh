@@ -33,6 +33,7 @@ struct DeviceInfo {
     bool prefill_attr_set = false;
     bool backward_attr_set = false;
     bool sgqa_attr_set = false;
+    bool mla_attr_set = false;
     void* legacy_ws = nullptr;  // scratch cached by the source-compatibility wrapper only
     size_t legacy_ws_bytes = 0;
 };

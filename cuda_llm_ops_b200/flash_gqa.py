@@ -324,6 +324,67 @@ def launch_flash_swa_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None
     return out_b, lse_b
 
 
+def launch_flash_mla_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None, causal=True, **_tuning):
+    """Mirror of upstream's MLA forward launcher (src/python/Triton/flash_mla_kernel.py:315-508).
+
+    The attention of ``launch_flash_gqa_forward_bf16_kernel`` with Q/K heads wider than V heads: q ``[.., seqlen_q,
+    head_dim_qk]``, k ``[.., seqlen_kv, head_dim_qk]``, v ``[.., seqlen_kv, head_dim_v]``, out ``[.., seqlen_q,
+    head_dim_v]``.  Same ranks, layouts, checks and return value ``(out, lse)`` as upstream; its Triton tuning keywords
+    are accepted and ignored.  This build supports head_dim_qk = 192 with head_dim_v = 128.
+    """
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("Flash MLA forward expects bf16 inputs")
+    if q.dim() not in (3, 4):
+        raise ValueError("Q must be 3D or 4D")
+    if k.dim() != q.dim() or v.dim() != q.dim():
+        raise ValueError("Q, K, and V must have matching ranks")
+    squeeze = q.dim() == 3
+    qb, kb, vb = (t.contiguous().unsqueeze(0) if squeeze else t.contiguous() for t in (q, k, v))
+    batch, q_heads, seqlen_q, head_dim_qk = qb.shape
+    _, num_kv_heads, seqlen_kv, k_head_dim = kb.shape
+    _, v_heads, v_seqlen, head_dim_v = vb.shape
+    if seqlen_kv != v_seqlen:
+        raise ValueError("K and V must share sequence length")
+    if k_head_dim != head_dim_qk:
+        raise ValueError("Q and K must share head_dim_qk")
+    if v_heads != num_kv_heads:
+        raise ValueError("K and V must share number of KV heads")
+    if q_heads % num_kv_heads != 0:
+        raise ValueError("Query heads must be divisible by KV heads")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t)
+    if head_dim_qk != 192 or head_dim_v != 128:
+        raise ValueError("this build supports head_dim_qk == 192 with head_dim_v == 128 only")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim_qk)
+    if out is None:
+        out_b = torch.empty((batch, q_heads, seqlen_q, head_dim_v), device=qb.device, dtype=qb.dtype)
+    else:
+        if out.dim() != q.dim():
+            raise ValueError("Output must be 3D when Q is 3D" if squeeze else "Output must be 4D when Q is 4D")
+        out_b = out.unsqueeze(0) if squeeze else out
+    if tuple(out_b.shape) != (batch, q_heads, seqlen_q, head_dim_v) or not out_b.is_contiguous():
+        raise ValueError("Output must have shape [batch, q_heads, seqlen_q, head_dim_v]")
+    if lse is None:
+        lse_b = torch.empty((batch, q_heads, seqlen_q), device=qb.device, dtype=torch.float32)
+    else:
+        if lse.dim() != q.dim() - 1:
+            raise ValueError("LSE must be 2D when Q is 3D" if squeeze else "LSE must be 3D when Q is 4D")
+        lse_b = lse.unsqueeze(0) if squeeze else lse
+    if tuple(lse_b.shape) != (batch, q_heads, seqlen_q) or not lse_b.is_contiguous() or lse_b.dtype != torch.float32:
+        raise ValueError("LSE must have shape [batch, q_heads, seqlen_q]")
+    if seqlen_q > 0:
+        with torch.cuda.device(qb.device):
+            rc = _lib.load().cllo_mla_prefill_fwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), float(scale),
+                                                       1 if causal else 0, out_b.data_ptr(), lse_b.data_ptr(), batch,
+                                                       seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
+                                                       head_dim_v, _stream_ptr())
+        _lib.check(rc, "cllo_mla_prefill_fwd_bf16")
+    if squeeze:
+        return out_b.squeeze(0), lse_b.squeeze(0)
+    return out_b, lse_b
+
+
 def launch_flash_sgqa_forward_bf16_kernel(q, k, v, sparse_kv_indices, num_sparse_kv, scale=None, out=None, lse=None,
                                           causal=True, block_sparse_sub=None, num_warps=None, num_stages=None):
     """Mirror of upstream's sparse-index GQA launcher (src/python/Triton/SparseGQA/flash_sgqa_kernel.py:202-396).

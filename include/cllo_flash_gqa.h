@@ -165,6 +165,17 @@ int cllo_swa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
 /*
+ * MLA-shaped attention forward (Q and K heads wider than V heads): O = softmax(mask(scale * Q K^T)) V, lse = m + log(l).
+ * Stands in for flash_mla_forward_bf16_kernel + launch_flash_mla_forward_bf16_kernel
+ * (src/python/Triton/flash_mla_kernel.py:16-268, :315-508).  Layout as upstream:
+ *   q [B,Hq,Sq,Dqk]   k [B,Hkv,Skv,Dqk]   v [B,Hkv,Skv,Dv]   o [B,Hq,Sq,Dv]   lse [B,Hq,Sq] fp32 (nullable)
+ * causal != 0 keeps kv <= q (top-left aligned).  Dqk = 192 and Dv = 128 (upstream's benchmark shape) only.
+ */
+int cllo_mla_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal,
+                              void* o, float* lse,
+                              int B, int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, void* stream);
+
+/*
  * Sparse-index GQA forward: every query token attends to its own list of kv tokens, shared by the query heads
  * of a group.  Stands in for flash_sgqa_forward_bf16_kernel + launch_flash_sgqa_forward_bf16_kernel
  * (src/python/Triton/SparseGQA/flash_sgqa_kernel.py:15-138, :202-396).

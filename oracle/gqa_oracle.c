@@ -278,6 +278,73 @@ int cllo_oracle_gqa_prefill_bf16(const uint16_t* q, const uint16_t* k, const uin
 }
 
 /*
+ * MLA-shaped forward: the same attention with head_dim_qk != head_dim_v, layout q [B,Hq,Sq,Dqk]; k [B,Hkv,Skv,Dqk];
+ * v [B,Hkv,Skv,Dv]; o [B,Hq,Sq,Dv]; lse [B,Hq,Sq].  Follows flash_mla_forward_reference of
+ * examples/python/Triton/test_flash_mla_kernel.py:27-94: fp32 scores = (q.k) * scale (:82), masked to -inf above the
+ * diagonal (:70-73,83), row max (:84), exp (:85), probabilities = exp / sum (:86), lse = log(sum) + max (:87),
+ * out = probs @ V in fp32 (:89), rounded to bf16 (:93-95).  Upstream's reference is causal-only; `causal == 0` skips
+ * the mask.
+ */
+int cllo_oracle_mla_prefill_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, float scale, int causal,
+                                 uint16_t* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Dqk <= 0 || Dv <= 0) return -1;
+    if (Hq % Hkv != 0) return -1;
+    const int G = Hq / Hkv;
+    const int64_t total = (int64_t)B * Hq * Sq;
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* sc = (float*)malloc(sizeof(float) * (size_t)Skv);
+        float* oacc = (float*)malloc(sizeof(float) * (size_t)Dv);
+        float* qf = (float*)malloc(sizeof(float) * (size_t)Dqk);
+        if (!sc || !oacc || !qf) {
+#pragma omp atomic write
+            failed = 1;
+        } else {
+#pragma omp for schedule(dynamic, 16)
+            for (int64_t idx = 0; idx < total; ++idx) {
+                const int64_t b = idx / ((int64_t)Hq * Sq);
+                const int64_t h = (idx / Sq) % Hq;
+                const int64_t i = idx % Sq;
+                const int64_t kvh = h / G;
+                const uint16_t* qrow = q + ((b * Hq + h) * Sq + i) * Dqk;
+                const uint16_t* kb = k + (b * Hkv + kvh) * (int64_t)Skv * Dqk;
+                const uint16_t* vb = v + (b * Hkv + kvh) * (int64_t)Skv * Dv;
+                int64_t n = Skv;
+                if (causal && i + 1 < n) n = i + 1;
+                for (int d = 0; d < Dqk; ++d) qf[d] = bf16_to_f32(qrow[d]);
+                float rmax = -INFINITY;
+                for (int64_t j = 0; j < n; ++j) {
+                    float acc = 0.f;
+                    const uint16_t* kr = kb + j * Dqk;
+                    for (int d = 0; d < Dqk; ++d) acc += qf[d] * bf16_to_f32(kr[d]);
+                    sc[j] = acc * scale;
+                    rmax = fmaxf(rmax, sc[j]);
+                }
+                float sum = 0.f;
+                for (int64_t j = 0; j < n; ++j) {
+                    sc[j] = expf(sc[j] - rmax);
+                    sum += sc[j];
+                }
+                for (int d = 0; d < Dv; ++d) oacc[d] = 0.f;
+                for (int64_t j = 0; j < n; ++j) {
+                    const float p = sc[j] / sum;
+                    const uint16_t* vr = vb + j * Dv;
+                    for (int d = 0; d < Dv; ++d) oacc[d] += p * bf16_to_f32(vr[d]);
+                }
+                if (o)
+                    for (int d = 0; d < Dv; ++d) o[((b * Hq + h) * Sq + i) * Dv + d] = f32_to_bf16(oacc[d]);
+                if (lse) lse[(b * Hq + h) * Sq + i] = logf(sum) + rmax;
+            }
+        }
+        free(sc);
+        free(oacc);
+        free(qf);
+    }
+    return failed ? -2 : 0;
+}
+
+/*
  * Sliding-window attention forward with a sink term, layout as the prefill oracle above.
  *
  * Follows examples/python/Triton/test_flash_swa_kernel.py:28-118: a query at position i sees kv in

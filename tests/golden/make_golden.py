@@ -14,6 +14,8 @@ It imports, unmodified,
   * ``flash_sgqa_forward_reference`` examples/python/Triton/test_flash_sgqa_kernel.py:102-216
     (sparse-index GQA; the list length is a module constant there, 512, which the script sets to the small
     length of its cases before calling the function),
+  * ``flash_mla_forward_reference``  examples/python/Triton/test_flash_mla_kernel.py:27-94
+    (head_dim_qk = 192, head_dim_v = 128, causal),
 feeds them small seeded N(0,1) bf16 tensors and stores inputs and outputs (bf16 as uint16 bit
 patterns) in ``gqa_golden.npz``.  The tests compare both the C oracle and the CUDA kernels with
 these files, so the oracle is pinned to upstream's own code rather than to itself.
@@ -157,6 +159,18 @@ def main():
         out[name + "/lse"] = lse.numpy().astype(np.float32)
         out[name + "/idx"] = idx.numpy().astype(np.int32)
         out[name + "/causal"] = np.array(1 if causal else 0)
+        meta.append(name)
+
+    # --- MLA-shaped forward (upstream flash_mla_forward_reference, test_flash_mla_kernel.py:27-94; causal) ---
+    from test_flash_mla_kernel import flash_mla_forward_reference  # noqa: E402
+    for i, (name, Hq, Hkv, S) in enumerate([("mla_g1", 2, 2, 200), ("mla_g2", 4, 2, 130)]):
+        g = torch.Generator().manual_seed(7000 + i)
+        q = torch.randn(Hq, S, 192, generator=g).to(torch.bfloat16)
+        k = torch.randn(Hkv, S, 192, generator=g).to(torch.bfloat16)
+        v = torch.randn(Hkv, S, 128, generator=g).to(torch.bfloat16)
+        o, lse = flash_mla_forward_reference(q, k, v, return_lse=True)
+        out[name + "/q"], out[name + "/k"], out[name + "/v"], out[name + "/o"] = map(_bits, (q, k, v, o))
+        out[name + "/lse"] = lse.numpy().astype(np.float32)
         meta.append(name)
 
     out["cases"] = np.array(meta)

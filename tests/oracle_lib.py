@@ -142,6 +142,21 @@ def swa_prefill(q, k, v, scale, window, sink):
     return o, lse
 
 
+def mla_prefill(q, k, v, scale, causal=True):
+    """MLA-shaped forward: q [B,Hq,Sq,Dqk], k [B,Hkv,Skv,Dqk], v [B,Hkv,Skv,Dv] uint16 -> (o [B,Hq,Sq,Dv] bits, lse)."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v))
+    B, Hq, Sq, Dqk = q.shape
+    _, Hkv, Skv, _ = k.shape
+    Dv = v.shape[3]
+    o = np.zeros((B, Hq, Sq, Dv), dtype=np.uint16)
+    lse = np.zeros((B, Hq, Sq), dtype=np.float32)
+    rc = lib().cllo_oracle_mla_prefill_bf16(
+        _ptr(q, ctypes.c_uint16), _ptr(k, ctypes.c_uint16), _ptr(v, ctypes.c_uint16), ctypes.c_float(scale),
+        1 if causal else 0, _ptr(o, ctypes.c_uint16), _ptr(lse, ctypes.c_float), B, Sq, Skv, Hq, Hkv, Dqk, Dv)
+    assert rc == 0, rc
+    return o, lse
+
+
 def sgqa_prefill(q, k, v, sparse_idx, scale, causal=True):
     """Sparse-index GQA forward: q [B,Hq,Sq,D], k,v [B,Hkv,Skv,D] uint16, sparse_idx int32 [B,Hkv,Sq,n] -> (o, lse)."""
     q, k, v = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q, k, v))

@@ -59,6 +59,24 @@ def test_swa_oracle_matches_upstream_torch_oracle(golden, name):
     assert np.allclose(got_lse[0], golden[name + "/lse"], atol=2e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["mla_g1", "mla_g2"])
+def test_mla_oracle_matches_upstream_torch_oracle(golden, name):
+    q, k, v, o = (golden[name + "/" + t][None] for t in ("q", "k", "v", "o"))
+    got_o, got_lse = ol.mla_prefill(q, k, v, 1.0 / np.sqrt(192.0), True)
+    mx, mean, rel = ol.errors(got_o, o)
+    assert mx <= 4e-3 and mean <= 2e-4 and rel <= 4e-3, (mx, mean, rel)
+    assert np.allclose(got_lse[0], golden[name + "/lse"], atol=2e-5, rtol=1e-5)
+
+
+def test_mla_oracle_with_equal_head_dims_is_the_gqa_oracle():
+    q = ol.randn_bf16((1, 4, 70, 128), 51)
+    k = ol.randn_bf16((1, 2, 70, 128), 52)
+    v = ol.randn_bf16((1, 2, 70, 128), 53)
+    a_o, a_lse = ol.mla_prefill(q, k, v, SCALE, True)
+    b_o, b_lse = ol.prefill(q, k, v, SCALE, True)
+    assert np.array_equal(a_o, b_o) and np.array_equal(a_lse, b_lse)
+
+
 @pytest.mark.parametrize("name", ["sgqa_g4_n40", "sgqa_g2_n16"])
 def test_sgqa_oracle_matches_upstream_torch_oracle(golden, name):
     q, k, v, o = (golden[name + "/" + t][None] for t in ("q", "k", "v", "o"))
