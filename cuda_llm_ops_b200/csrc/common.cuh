@@ -116,9 +116,11 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tmap, uint32_t s
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
+// Waits only until the copy engine has READ the shared-memory source: the block may then retire (or reuse the
+// buffer) while the global writes drain like any other store.
 __device__ __forceinline__ void tma_store_commit_and_wait() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
