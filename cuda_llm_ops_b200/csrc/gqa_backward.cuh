@@ -143,15 +143,43 @@ __device__ __forceinline__ void init_bars(const Bars& bars) {
 // ------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------
+// Pipelined over the kv tiles through tensor memory: S(j) and dP(j) land in two fixed regions, the element-wise threads
+// copy them to registers at once and hand the regions back, so S(j+1), dP(j+1) are computed while dS(j) is being
+// formed; dS has two homes, so dQ += dS(j) K(j) runs while dS(j+1) is written.
+//   tensor memory: S (128) | dP (128) | dS[0] (64) | dS[1] (64) | dQ (128)
+//   shared memory: Q, dO (fixed) | K x 3 stages (a K tile is still needed by the late dQ product) | V x 2 stages
+namespace dq {
+constexpr int kKStages = 3;
+constexpr int kVStages = 2;
+constexpr int kSmemK = 2 * kTileBytes;
+constexpr int kSmemV = kSmemK + kKStages * kTileBytes;
+constexpr int kSmemBar = kSmemV + kVStages * kTileBytes;  // 224 KB
+constexpr int kNumBars = 20;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+constexpr uint32_t kColS = 0, kColDP = 128, kColDS = 256, kColDQ = 384;
+struct Bars {
+    uint32_t base;
+    __device__ uint32_t fixed_full() const { return base; }
+    __device__ uint32_t k_full(int s) const { return base + 8 * (1 + s); }
+    __device__ uint32_t v_full(int s) const { return base + 8 * (4 + s); }
+    __device__ uint32_t k_empty(int s) const { return base + 8 * (6 + s); }   // dQ(j) retired: K stage j % 3 free
+    __device__ uint32_t sdp_full(int s) const { return base + 8 * (9 + s); }  // S(j), dP(j) landed (j % 2); V stage free
+    __device__ uint32_t ds_full(int s) const { return base + 8 * (11 + s); }  // dS[j % 2] stored
+    __device__ uint32_t dq_done(int s) const { return base + 8 * (13 + s); }  // dQ(j) retired: dS[j % 2] free
+    __device__ uint32_t c_free() const { return base + 8 * 15; }              // S, dP of step j copied to registers
+    __device__ uint32_t drain() const { return base + 8 * 16; }
+};
+}  // namespace dq
+
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const Bars bars{base + kSmemBar};
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
+    const dq::Bars bars{base + dq::kSmemBar};
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + dq::kSmemBar + dq::kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + dq::kSmemBar + dq::kNumBars * 8 + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     long long id = blockIdx.x;
@@ -174,10 +202,46 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (j_lo > j_hi - 1) j_lo = j_hi - 1;
     const int n_kv = j_hi - j_lo;
 
-    if (threadIdx.x == 0) {
-        init_bars(bars);
+    const uint32_t sm_q = base, sm_do = base + kTileBytes;
+    auto sm_k = [&](int s) { return base + dq::kSmemK + s * kTileBytes; };
+    auto sm_v = [&](int s) { return base + dq::kSmemV + s * kTileBytes; };
+    auto load_k = [&](int j) {
+        const int s = j % dq::kKStages;
+        mbar_arrive_expect_tx(bars.k_full(s), kTileBytes);
+        tma_load_4d(sm_k(s), &tm_k, bars.k_full(s), 0, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.k_full(s), 64, (j_lo + j) * kBN, kvh, b);
+    };
+    auto load_v = [&](int j) {
+        const int s = j % dq::kVStages;
+        mbar_arrive_expect_tx(bars.v_full(s), kTileBytes);
+        tma_load_4d(sm_v(s), &tm_v, bars.v_full(s), 0, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.v_full(s), 64, (j_lo + j) * kBN, kvh, b);
+    };
+
+    if (warp == 8 && lane == 0) {
+        mbar_init(bars.fixed_full(), 1);
+        for (int s = 0; s < 3; ++s) {
+            mbar_init(bars.k_full(s), 1);
+            mbar_init(bars.k_empty(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bars.v_full(s), 1);
+            mbar_init(bars.sdp_full(s), 1);
+            mbar_init(bars.ds_full(s), 2 * kBM);
+            mbar_init(bars.dq_done(s), 1);
+        }
+        mbar_init(bars.c_free(), 2 * kBM);
+        mbar_init(bars.drain(), 1);
         *abort_flag = 0;
         fence_mbar_init();
+        // the first copies start before the block has met at its first barrier
+        mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
+        tma_load_4d(sm_q, &tm_q, bars.fixed_full(), 0, q0, h, b);
+        tma_load_4d(sm_q + kHalfBytes, &tm_q, bars.fixed_full(), 64, q0, h, b);
+        tma_load_4d(sm_do, &tm_do, bars.fixed_full(), 0, q0, h, b);
+        tma_load_4d(sm_do + kHalfBytes, &tm_do, bars.fixed_full(), 64, q0, h, b);
+        load_k(0);
+        load_v(0);
     }
     if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -187,69 +251,95 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;
-    const uint32_t sm_q = base, sm_do = base + kTileBytes;
-    auto sm_k = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes; };
-    auto sm_v = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes + kTileBytes; };
+    const uint32_t tm_s = tmem_base + dq::kColS, tm_dp = tmem_base + dq::kColDP, tm_dq = tmem_base + dq::kColDQ;
 
     if (warp == 8) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
-            tma_load_4d(sm_q, &tm_q, bars.fixed_full(), 0, q0, h, b);
-            tma_load_4d(sm_q + kHalfBytes, &tm_q, bars.fixed_full(), 64, q0, h, b);
-            tma_load_4d(sm_do, &tm_do, bars.fixed_full(), 0, q0, h, b);
-            tma_load_4d(sm_do + kHalfBytes, &tm_do, bars.fixed_full(), 64, q0, h, b);
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j % kStages;
-                const uint32_t use = static_cast<uint32_t>(j / kStages);
-                // K of a stage is released by the dQ product, V earlier by the dP product
-                mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
-                mbar_wait(bars.aux_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, j);
-                mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
-                tma_load_4d(sm_k(s), &tm_k, bars.stream_full(s), 0, (j_lo + j) * kBN, kvh, b);
-                tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.stream_full(s), 64, (j_lo + j) * kBN, kvh, b);
-                tma_load_4d(sm_v(s), &tm_v, bars.stream_full(s), 0, (j_lo + j) * kBN, kvh, b);
-                tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.stream_full(s), 64, (j_lo + j) * kBN, kvh, b);
+            for (int j = 1; j < n_kv; ++j) {
+                if (j >= dq::kKStages)  // stage j % 3 held K(j-3): free once dQ(j-3) has retired
+                    mbar_wait(bars.k_empty(j % dq::kKStages), static_cast<uint32_t>((j - 3) / 3) & 1u, abort_flag,
+                              SITE_BWD_STREAM_EMPTY, j);
+                load_k(j);
+                if (j >= dq::kVStages)  // stage j % 2 held V(j-2): free once dP(j-2) has retired
+                    mbar_wait(bars.sdp_full(j & 1), static_cast<uint32_t>((j - 2) >> 1) & 1u, abort_flag,
+                              SITE_BWD_STREAM_EMPTY, j);
+                load_v(j);
             }
             if (*abort_flag) {
-                for (int j = (n_kv > kStages ? n_kv - kStages : 0); j < n_kv; ++j) {
+                for (int j = (n_kv > 2 ? n_kv - 2 : 0); j < n_kv; ++j) {
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(bars.stream_full(j % kStages), static_cast<uint32_t>(j / kStages) & 1u) &&
+                    while (!(mbar_try_wait(bars.k_full(j % 3), static_cast<uint32_t>(j / 3) & 1u) &&
+                             mbar_try_wait(bars.v_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u)) &&
                            clock64() - t0 < kWaitLimitCycles / 64) {
                     }
                 }
             }
         }
     } else if (warp == 9) {
+        // One thread issues every MMA; per kv tile one run of 16 (S and dP of the NEXT tile) and one of 8 (dQ of this
+        // tile), each behind one look at its barriers (the whole warp looks at once, one barrier per lane).
+        auto issue_sdp = [&](int j) {
+            const uint32_t ka = sm_k(j % dq::kKStages), va = sm_v(j & 1);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // S = Q K^T
+                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                tc_mma_ss(tm_s, smem_desc(sm_q + off, 16, 1024), smem_desc(ka + off, 16, 1024), kIdescQK,
+                          ks > 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // dP = dO V^T
+                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                tc_mma_ss(tm_dp, smem_desc(sm_do + off, 16, 1024), smem_desc(va + off, 16, 1024), kIdescQK,
+                          ks > 0 ? 1u : 0u);
+            }
+        };
         if (lane == 0) {
             mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j % kStages;
-                const uint32_t use = static_cast<uint32_t>(j / kStages);
-                mbar_wait(bars.stream_full(s), use & 1u, abort_flag, SITE_BWD_STREAM_FULL, j);
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // S = Q K^T
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tm_s, smem_desc(sm_q + off, 16, 1024), smem_desc(sm_k(s) + off, 16, 1024), kIdescQK,
-                              ks > 0 ? 1u : 0u);
+            mbar_wait(bars.k_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
+            mbar_wait(bars.v_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
+            tc_fence_after();
+            issue_sdp(0);
+            tc_commit(bars.sdp_full(0));
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int j = 0; j < n_kv; ++j) {
+            if (j + 1 < n_kv) {
+                // lane 0: S, dP of tile j copied out; 1: K(j+1) arrived; 2: V(j+1) arrived
+                uint32_t my_bar = bars.c_free(), my_par = static_cast<uint32_t>(j) & 1u;
+                if (lane == 1) {
+                    my_bar = bars.k_full((j + 1) % dq::kKStages);
+                    my_par = static_cast<uint32_t>((j + 1) / 3) & 1u;
+                } else if (lane == 2) {
+                    my_bar = bars.v_full((j + 1) & 1);
+                    my_par = static_cast<uint32_t>((j + 1) >> 1) & 1u;
                 }
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // dP = dO V^T
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tm_dp, smem_desc(sm_do + off, 16, 1024), smem_desc(sm_v(s) + off, 16, 1024), kIdescQK,
-                              ks > 0 ? 1u : 0u);
+                if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                    if (lane < 3) mbar_wait(my_bar, my_par, abort_flag, SITE_BWD_STREAM_FULL, j);
+                    __syncwarp();
                 }
-                tc_commit(bars.s_full());
-                tc_commit(bars.aux_empty(s));
-                mbar_wait(bars.ds_full(), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
+                if (lane == 0) {
+                    tc_fence_after();
+                    issue_sdp(j + 1);
+                    tc_commit(bars.sdp_full((j + 1) & 1));
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                mbar_wait(bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
                 tc_fence_after();
+                const uint32_t ka = sm_k(j % dq::kKStages);
+                const uint32_t dsa = tmem_base + dq::kColDS + (j & 1) * 64;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)  // dQ += dS K   (K tile as the MN-major B operand)
-                    tc_mma_ts(tm_dq, tm_s + a_col(ks), smem_desc(sm_k(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
+                    tc_mma_ts(tm_dq, dsa + ks * 8, smem_desc(ka + ks * 2048, kHalfBytes, 1024), kIdescPV,
                               (j == 0 && ks == 0) ? 0u : 1u);
-                tc_commit(bars.stream_empty(s));
+                tc_commit(bars.dq_done(j & 1));
+                tc_commit(bars.k_empty(j % dq::kKStages));
             }
+            __syncwarp();
+        }
+        if (lane == 0) {
             tc_commit(bars.drain());
             mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 0);
             if (*abort_flag) {
@@ -271,9 +361,30 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const float c = p.scale * kLog2e;
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
-            mbar_wait(bars.s_full(), static_cast<uint32_t>(j) & 1u, abort_flag, SITE_BWD_S_FULL, j);
+            mbar_wait(bars.sdp_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_S_FULL, j);
             __syncwarp();
             tc_fence_after();
+            float sv[64], dpv[64];
+            {
+                float t0[32], t1[32];
+                tmem_ld32_wait(tm_s + lane_base + half * 64, t0);
+                tmem_ld32_wait(tm_s + lane_base + half * 64 + 32, t1);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    sv[e] = t0[e];
+                    sv[32 + e] = t1[e];
+                }
+                tmem_ld32_wait(tm_dp + lane_base + half * 64, t0);
+                tmem_ld32_wait(tm_dp + lane_base + half * 64 + 32, t1);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    dpv[e] = t0[e];
+                    dpv[32 + e] = t1[e];
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bars.c_free());  // both regions are in registers: the next tile's S and dP may land
+
             // columns this row may see in this tile (only diagonal and tail tiles need the test)
             const int kvt0 = (j_lo + j) * kBN;  // first kv position of this tile
             int limit = p.Skv - 1 - kvt0;
@@ -287,32 +398,32 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse2, -lse2);
             const uint64_t sc2 = pk2(p.scale, p.scale), nds2 = pk2(-drow * p.scale, -drow * p.scale);
             uint32_t pk[32];
+            const int col0 = half * 64;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                const int col0 = half * 64 + cc * 32;
-                float sv[32], dpv[32];
-                tmem_ld32_wait(tm_s + lane_base + col0, sv);
-                tmem_ld32_wait(tm_dp + lane_base + col0, dpv);
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float y0, y1;
-                    upk2(fma2(pk2(sv[e], sv[e + 1]), c2, nl2), y0, y1);
-                    float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-                    if (need_mask) {
-                        p0 = (col0 + e <= limit && col0 + e >= first) ? p0 : 0.f;
-                        p1 = (col0 + e + 1 <= limit && col0 + e + 1 >= first) ? p1 : 0.f;
-                    }
-                    // dS = P * (dP - D) * scale
-                    float d0, d1;
-                    upk2(mul2(pk2(p0, p1), fma2(pk2(dpv[e], dpv[e + 1]), sc2, nds2)), d0, d1);
-                    pk[cc * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+            for (int e = 0; e < 64; e += 2) {
+                float y0, y1;
+                upk2(fma2(pk2(sv[e], sv[e + 1]), c2, nl2), y0, y1);
+                float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                if (need_mask) {
+                    p0 = (col0 + e <= limit && col0 + e >= first) ? p0 : 0.f;
+                    p1 = (col0 + e + 1 <= limit && col0 + e + 1 >= first) ? p1 : 0.f;
                 }
+                // dS = P * (dP - D) * scale
+                float d0, d1;
+                upk2(mul2(pk2(p0, p1), fma2(pk2(dpv[e], dpv[e + 1]), sc2, nds2)), d0, d1);
+                pk[e >> 1] = pack_bf16x2(d0, d1);
             }
-            // dS (bf16) over the first 32 columns of this warpgroup's own half of S
-            tmem_st32(tm_s + lane_base + half * 64, pk);
+            // dS[j % 2] still feeds dQ += dS(j-2) K(j-2) until that product has retired
+            if (j >= 2) {
+                mbar_wait(bars.dq_done(j & 1), static_cast<uint32_t>((j - 2) >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
+                __syncwarp();
+                tc_fence_after();
+            }
+            // dS (bf16): this half's 64 values are columns [32 * half, 32 * half + 32) of dS[j % 2]
+            tmem_st32(tmem_base + dq::kColDS + (j & 1) * 64 + lane_base + half * 32, pk);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bars.ds_full());
+            mbar_arrive(bars.ds_full(j & 1));
         }
         // epilogue: dQ -> bf16
         mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 1);
@@ -689,7 +800,7 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     if ((rc = prefill::encode_bhsd_map(&tm_do, grad_o, B, Hq, Sq)) != CLLO_OK) return rc;
 
     if (!di->backward_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::kSmemBytes));
         CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         di->backward_attr_set = true;
     }
@@ -697,7 +808,7 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
         static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(grad_o), static_cast<float*>(workspace),
         rows);
     CLLO_CUDA_TRY(cudaGetLastError());
-    bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
+    bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, dq::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
