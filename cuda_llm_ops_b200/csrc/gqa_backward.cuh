@@ -4,7 +4,7 @@
 //                     S = Q K^T and dP = dO V^T into tensor memory; 256 threads turn them into
 //                     dS = P o (dP - D) * scale with P = exp(scale*S - lse) (no row reduction: the forward
 //                     pass left lse, a small pre-pass leaves D = rowsum(dO o O)); dS goes back to tensor
-//                     memory as bf16 and feeds dQ += dS K as the A operand.
+//                     memory as bf16 (a region of its own, two buffers) and feeds dQ += dS K as the A operand.
 //   bwd_dkdv_kernel   one block per (batch, kv head, 128 kv rows); loops over all query tiles of all heads
 //                     of the group.  It forms the TRANSPOSED tiles directly, S^T = K Q^T and
 //                     dP^T = V dO^T, so that P^T and dS^T are again A operands in tensor memory for
@@ -15,8 +15,8 @@
 //                     go to the workspace and bwd_reduce_kernel sums them in a fixed order.
 //
 // Both recompute S and dP (7 tile products per (q tile, kv tile) instead of the minimal 5); in exchange no
-// gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dQ (384 of 512 columns),
-// dK/dV kernel S^T | dP^T | dV | dK (all 512).  Shared-memory operand layouts, descriptors, TMA boxes and
+// gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dS[0] | dS[1] | dQ (pipelined over the
+// kv tiles, see there), dK/dV kernel S^T | dP^T | dV | dK (all 512, P^T and dS^T written over S^T and dP^T).  Shared-memory operand layouts, descriptors, TMA boxes and
 // barrier conventions are those of the forward kernel (gqa_prefill.cuh).
 //
 // Upstream: flash_gqa_backward_bf16_kernel, src/python/Triton/flash_gqa_backward_kernel.py:159-310 (one
