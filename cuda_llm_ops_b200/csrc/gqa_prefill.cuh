@@ -60,7 +60,6 @@ constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kDefaultEmu8 = 0;
 
 enum : int {
     SITE_Q_FULL = SITE_PREFILL_BASE + 0,
@@ -305,28 +304,6 @@ __device__ __forceinline__ void exp2_pair_sfu(uint64_t y, float& p0, float& p1) 
     p0 = fast_exp2(a);
     p1 = fast_exp2(b);
 }
-// 2^y for a pair, on the FMA pipes: y = i + f with i = round(y), f in [-0.5, 0.5]; 2^f by a cubic
-// (max relative error 7.5e-5, far below the bf16 rounding of P); 2^i by adding i to the exponent field.
-// The special-function unit delivers 16 results per clock per SM, which for this kernel is as scarce as
-// the tensor pipe, so a fixed share of the exponentials is computed this way.
-__device__ __forceinline__ void exp2_pair_fma(uint64_t y, float& p0, float& p1) {
-    float a, b;
-    upk2(y, a, b);
-    a = fmaxf(a, -126.f);  // also turns -inf (masked) into a denormal-sized result
-    b = fmaxf(b, -126.f);
-    const uint64_t yy = pk2(a, b);
-    const uint64_t t = add2(yy, pk2(12582912.f, 12582912.f));  // 1.5 * 2^23: integer part lands in the low mantissa bits
-    const uint64_t r = add2(t, pk2(-12582912.f, -12582912.f));
-    const uint64_t f = fma2(r, pk2(-1.f, -1.f), yy);
-    uint64_t q = fma2(f, pk2(0.0551716648f, 0.0551716648f), pk2(0.2426111251f, 0.2426111251f));
-    q = fma2(q, f, pk2(0.6932609677f, 0.6932609677f));
-    q = fma2(q, f, pk2(0.9999280572f, 0.9999280572f));
-    float q0, q1, t0, t1;
-    upk2(q, q0, q1);
-    upk2(t, t0, t1);
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-}
 
 // Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes.
 //   bits [0,14) start >> 4 | [16,30) leading-dim offset >> 4 | [32,46) stride-dim offset >> 4
@@ -345,9 +322,6 @@ __host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo) { return ((sbo
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 
-// kEmu8: of every 8 pairs of exponentials, this many are computed on the FMA pipes instead of the
-// special-function unit.
-template <int kEmu8>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -748,10 +722,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 const int col = e * 2;
                 const uint64_t y = fma2(pk2(x[col], x[col + 1]), c2, nm2);
                 float p0, p1;
-                if ((e * kEmu8) % 8 < kEmu8)
-                    exp2_pair_fma(y, p0, p1);
-                else
-                    exp2_pair_sfu(y, p0, p1);
+                exp2_pair_sfu(y, p0, p1);
                 sum2 = add2(sum2, pk2(p0, p1));
                 pk[e] = pack_bf16x2(p0, p1);
             }
@@ -866,37 +837,17 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     if ((rc = encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
     if ((rc = encode_bhsd_map(&tm_o, o, B, Hq, Sq)) != CLLO_OK) return rc;
 
-    // share of exponentials moved to the FMA pipes, in eighths (tuning knob; default chosen by measurement)
-    static const int emu8 = [] {
-        const char* e = std::getenv("CLLO_PREFILL_EMU8");
-        const int v = e ? std::atoi(e) : kDefaultEmu8;
-        return (v == 0 || v == 2 || v == 3 || v == 4) ? v : kDefaultEmu8;
-    }();
     if (!di->prefill_attr_set) {
         // the register re-balancing inside the kernel assumes the pool the kernel is launched with: refuse to
         // launch (rather than block inside setmaxnreg) if the compiler gave the kernel fewer registers
-        const void* fns[4] = {reinterpret_cast<const void*>(prefill_fwd_kernel<0>),
-                              reinterpret_cast<const void*>(prefill_fwd_kernel<2>),
-                              reinterpret_cast<const void*>(prefill_fwd_kernel<3>),
-                              reinterpret_cast<const void*>(prefill_fwd_kernel<4>)};
-        for (const void* fn : fns) {
-            cudaFuncAttributes fa;
-            CLLO_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
-            if (fa.numRegs < kLaunchRegs) return CLLO_E_UNSUPPORTED;
-        }
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        cudaFuncAttributes fa;
+        CLLO_CUDA_TRY(cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(prefill_fwd_kernel)));
+        if (fa.numRegs < kLaunchRegs) return CLLO_E_UNSUPPORTED;
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(prefill_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         di->prefill_attr_set = true;
     }
     const unsigned grid = static_cast<unsigned>(blocks);
-    switch (emu8) {
-        case 0: prefill_fwd_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
-        case 2: prefill_fwd_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
-        case 3: prefill_fwd_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
-        default: prefill_fwd_kernel<4><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p); break;
-    }
+    prefill_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }

@@ -10,7 +10,7 @@
 // by the tensor cores.  Hence no tcgen05 here (its M is 128; a token offers 16 rows and no two tokens share an
 // operand): ONE WARP owns one token at a time and needs nobody else --
 //   * it gathers 16 list entries at a time (16 K rows + 16 V rows = 8 KB) with 16-byte cp.async copies into its
-//     private shared-memory ring (three buffers, two gathers in flight), in the swizzled [row][128 B] layout that
+//     private shared-memory ring (two buffers: the next gather is in flight while this one is used), in the swizzled [row][128 B] layout that
 //     ldmatrix reads without bank conflicts; entries that are out of range, negative (padding) or above the
 //     query position (causal) are zero-filled and masked, a group of 16 without any valid entry is skipped;
 //   * S = Q K^T (16 heads x 16 entries) and O += P V by mma.sync m16n8k16 with the online softmax in registers
@@ -21,8 +21,6 @@
 
 #include "common.cuh"
 #include "host_util.cuh"
-
-#include <cstdlib>
 
 namespace cllo {
 namespace sgqa {
@@ -312,28 +310,17 @@ static int launch(const void* q, const void* k, const void* v, const int* idx, i
     p.num_sparse = num_sparse;
     p.n_tokens = static_cast<long long>(B) * Hkv * Sq;
 
-    // warps per block x ring depth (tuning knob; the default was chosen by measurement)
-    static const int cfg = [] {
-        const char* e = std::getenv("CLLO_SGQA_CFG");
-        const int v = e ? std::atoi(e) : 0;
-        return (v == 83 || v == 122 || v == 142 || v == 102) ? v : kDefaultWarps * 10 + kDefaultBufs;
-    }();
-    auto run = [&](auto kernel, int warps, int bufs) -> int {
-        const int smem = smem_bytes(warps, bufs);
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        const long long want = (p.n_tokens + warps - 1) / warps;
-        const long long cap = static_cast<long long>(di->sm_count) * 8;  // a few rounds per SM: lists differ in length
-        const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-        kernel<<<grid, warps * 32, smem, stream>>>(p);
-        return CLLO_OK;
-    };
-    switch (cfg) {
-        case 142: rc = run(sgqa_fwd_kernel<14, 2>, 14, 2); break;
-        case 102: rc = run(sgqa_fwd_kernel<10, 2>, 10, 2); break;
-        case 83: rc = run(sgqa_fwd_kernel<8, 3>, 8, 3); break;
-        default: rc = run(sgqa_fwd_kernel<12, 2>, 12, 2); break;
+    // 12 warps x 2 ring buffers (192 KB) measured best at upstream's shape: 8 x 3 1041 us, 10 x 2 1197, 12 x 2 838,
+    // 14 x 2 1039 (128 registers per thread: spills)
+    constexpr int warps = kDefaultWarps, bufs = kDefaultBufs, smem = smem_bytes(kDefaultWarps, kDefaultBufs);
+    if (!di->sgqa_attr_set) {
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(sgqa_fwd_kernel<warps, bufs>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        di->sgqa_attr_set = true;
     }
-    if (rc != CLLO_OK) return rc;
+    const long long want = (p.n_tokens + warps - 1) / warps;
+    const long long cap = static_cast<long long>(di->sm_count) * 8;  // a few rounds per SM: lists differ in length
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    sgqa_fwd_kernel<warps, bufs><<<grid, warps * 32, smem, stream>>>(p);
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }
