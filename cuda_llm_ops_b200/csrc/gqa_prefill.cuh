@@ -297,6 +297,18 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// three-input maximum / minimum (one instruction on this architecture)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // 2^y for a pair, on the special-function unit
 __device__ __forceinline__ void exp2_pair_sfu(uint64_t y, float& p0, float& p1) {
     float a, b;
@@ -663,13 +675,24 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 for (int c = 0; c < 128; ++c)
                     if (c > limit || c < first) x[c] = masked;
             }
+            // (three-input min/max: 64 instructions for the 128 scores instead of 128)
             float e0 = neg ? INFINITY : -INFINITY, e1 = e0, e2 = e0, e3 = e0;
+            if (neg) {
 #pragma unroll
-            for (int c = 0; c < 128; c += 4) {
-                e0 = neg ? fminf(e0, x[c]) : fmaxf(e0, x[c]);
-                e1 = neg ? fminf(e1, x[c + 1]) : fmaxf(e1, x[c + 1]);
-                e2 = neg ? fminf(e2, x[c + 2]) : fmaxf(e2, x[c + 2]);
-                e3 = neg ? fminf(e3, x[c + 3]) : fmaxf(e3, x[c + 3]);
+                for (int c = 0; c < 128; c += 8) {
+                    e0 = min3(e0, x[c], x[c + 1]);
+                    e1 = min3(e1, x[c + 2], x[c + 3]);
+                    e2 = min3(e2, x[c + 4], x[c + 5]);
+                    e3 = min3(e3, x[c + 6], x[c + 7]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 128; c += 8) {
+                    e0 = max3(e0, x[c], x[c + 1]);
+                    e1 = max3(e1, x[c + 2], x[c + 3]);
+                    e2 = max3(e2, x[c + 4], x[c + 5]);
+                    e3 = max3(e3, x[c + 6], x[c + 7]);
+                }
             }
             e0 = neg ? fminf(e0, e1) : fmaxf(e0, e1);
             e2 = neg ? fminf(e2, e3) : fmaxf(e2, e3);
