@@ -33,6 +33,47 @@ def test_triton_prefill_launcher_error_behaviour_matches_upstream():
         ops.launch_flash_gqa_forward_bf16_kernel(_t(4, 8, 128), _t(1, 1, 8, 128), _t(1, 8, 128))
 
 
+def test_sparse_and_mla_launcher_error_behaviour_matches_upstream():
+    """Argument checks of the sparse-index and MLA launchers, in upstream's order and wording, before any device work."""
+    import torch
+    import cuda_llm_ops_b200 as ops
+    q = torch.zeros((1, 4, 8, 128), dtype=torch.bfloat16)
+    k = torch.zeros((1, 2, 8, 128), dtype=torch.bfloat16)
+    idx = torch.zeros((1, 2, 8, 4), dtype=torch.int32)
+    with pytest.raises(ValueError, match="expects bf16 inputs"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q.float(), k, k, idx, 4)
+    with pytest.raises(ValueError, match="must be int32"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx.long(), 4)
+    with pytest.raises(ValueError, match="must be 4D"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx[0], 4)
+    with pytest.raises(ValueError, match="num_sparse_kv must be an int"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx, 4.0)
+    with pytest.raises(ValueError, match="block_sparse_sub"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx, 4, block_sparse_sub=0)
+    with pytest.raises(ValueError, match="matching ranks"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k[0], k, idx, 4)
+    with pytest.raises(ValueError, match="must have shape"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx, 3)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.launch_flash_sgqa_forward_bf16_kernel(q, k, k, idx, 4)
+
+    qm = torch.zeros((4, 8, 192), dtype=torch.bfloat16)
+    km = torch.zeros((2, 8, 192), dtype=torch.bfloat16)
+    vm = torch.zeros((2, 8, 128), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="expects bf16 inputs"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm.float(), km, vm)
+    with pytest.raises(ValueError, match="share head_dim_qk"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm, km[..., :128], vm)
+    with pytest.raises(ValueError, match="share sequence length"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm, km, vm[:, :4])
+    with pytest.raises(ValueError, match="number of KV heads"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm, km, vm[:1])
+    with pytest.raises(ValueError, match="divisible by KV heads"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm[:3], km, vm)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.launch_flash_mla_forward_bf16_kernel(qm, km, vm)
+
+
 def test_no_cpu_path():
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.gqa_decode(_t(1, 4, 128), _t(1, 1, 8, 128), _t(1, 1, 8, 128))
