@@ -74,6 +74,19 @@ def test_large_scores_exercise_the_rescaling_of_o():
     assert_clean_status()
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_negative_scale(causal):
+    B, Hq, Hkv, Sq, Skv = 1, 4, 2, 300, 420
+    q = ol.randn_bf16((B, Hq, Sq, 192), 421)
+    k = ol.randn_bf16((B, Hkv, Skv, 192), 422)
+    v = ol.randn_bf16((B, Hkv, Skv, 128), 423)
+    want_o, want_lse = ol.mla_prefill(q, k, v, -SCALE, causal)
+    got_o, got_lse = _run(q, k, v, causal, scale=-SCALE)
+    ol.assert_parity(got_o, want_o, "negative scale causal=%d" % causal)
+    assert np.allclose(got_lse, want_lse, atol=2e-3), np.abs(got_lse - want_lse).max()
+    assert_clean_status()
+
+
 def test_upstream_shape_sampled_rows():
     """Upstream's benchmark shape (S = 4096, 16 heads, no grouping), rows checked by sampling."""
     import cuda_llm_ops_b200 as ops

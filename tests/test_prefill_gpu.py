@@ -75,6 +75,20 @@ def test_peaked_scores_exercise_the_rescale_path():
     assert_clean_status()
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_negative_scale_turns_the_row_maximum_into_a_minimum(causal):
+    """The kernel takes the row extreme on the raw scores; with a negative scale that is the minimum."""
+    B, Hq, Hkv, Sq, Skv = 1, 4, 2, 384, 500
+    q = ol.randn_bf16((B, Hq, Sq, 128), 121)
+    k = ol.randn_bf16((B, Hkv, Skv, 128), 122)
+    v = ol.randn_bf16((B, Hkv, Skv, 128), 123)
+    want_o, want_lse = ol.prefill(q, k, v, -SCALE, causal)
+    got_o, got_lse = _run(q, k, v, causal, scale=-SCALE)
+    ol.assert_parity(got_o, want_o, "negative scale causal=%d" % causal)
+    assert np.allclose(got_lse, want_lse, atol=LSE_TOL), np.abs(got_lse - want_lse).max()
+    assert_clean_status()
+
+
 def test_headline_prefill_shape_sampled_rows():
     """Baseline config 3 (B=1, S=4096, Hq=16, Hkv=1, non-causal) at full size; rows sampled for the oracle."""
     import cuda_llm_ops_b200 as ops
