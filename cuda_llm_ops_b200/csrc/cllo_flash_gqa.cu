@@ -184,6 +184,10 @@ int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer
 
 int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
                               float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+    // all query rows in one 128-row tile (chunked prefill, a few decode tokens): the one-tile kernel, which does not
+    // spend half its work on an empty second tile
+    if (D == 128 && Sq > 0 && Sq <= 128)
+        return mla::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D, D, static_cast<cudaStream_t>(stream));
     return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D,
                            static_cast<cudaStream_t>(stream));
 }

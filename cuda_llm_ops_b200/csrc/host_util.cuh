@@ -34,6 +34,7 @@ struct DeviceInfo {
     bool backward_attr_set = false;
     bool sgqa_attr_set = false;
     bool mla_attr_set = false;
+    bool one_tile_attr_set = false;
     void* legacy_ws = nullptr;  // scratch cached by the source-compatibility wrapper only
     size_t legacy_ws_bytes = 0;
 };

@@ -7,11 +7,13 @@
 // no longer fits shared memory (2 Q tiles + 2 K stages + 2 V stages = 256 KB).  Here a block owns ONE 128-row
 // query tile and pipelines over the kv tiles instead, which tensor memory allows once S and P have two homes each:
 //     tensor memory (512 columns): C0 (128) | C1 (128) | P0 (64) | P1 (64) | O (128)
-//     S(j) = Q K(j)^T lands in C[j % 2] (12 MMAs M128 N128 K16, Q and K K-major from shared memory); the 128 softmax
+//     S(j) = Q K(j)^T lands in C[j % 2] (12 MMAs M128 N128 K16 at a 192-wide head, Q and K K-major from shared memory); the 128 softmax
 //     threads copy it to registers at once and hand the region back, so S(j+2) can follow while softmax(j) and
 //     softmax(j+1) run; P(j) goes to P[j % 2] as bf16 and O += P(j) V(j) (8 MMAs, A from tensor memory, V MN-major)
 //     has until softmax(j+2) wants that region again.
 // Shared memory: Q 48 KB (three [128][64] slabs, 128-byte swizzle), K 2 x 48 KB, V 2 x 32 KB.
+// The kernel is a template on the Q/K head width; the 128-wide instance serves the GQA forward when all query rows fit
+// one tile (Sq <= 128: decode-like chunks), where the two-tile kernel would spend half its work on an empty tile.
 // Warps: 0-3 softmax (one query row per thread), 4 TMA producer, 5 MMA issuer, 6-7 idle.  Barrier conventions,
 // bounded waits and the status word are those of the GQA forward kernel; so are the lazy rescaling, the packed
 // fp32 arithmetic and the bulk-store epilogue.
@@ -48,21 +50,25 @@ using prefill::tmem_st32;
 using prefill::tmem_wait_st;
 using prefill::upk2;
 
-constexpr int kDqk = 192;
 constexpr int kDv = 128;
 constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kThreads = 256;
 constexpr int kSlabBytes = 128 * 128;              // [128 rows][64 dims] bf16, one swizzled slab
-constexpr int kQBytes = 3 * kSlabBytes;            // 48 KB
-constexpr int kKBytes = 3 * kSlabBytes;
 constexpr int kVBytes = 2 * kSlabBytes;
-constexpr int kSmemQ = 0;
-constexpr int kSmemK = kQBytes;
-constexpr int kSmemV = kSmemK + 2 * kKBytes;
-constexpr int kSmemBar = kSmemV + 2 * kVBytes;     // 208 KB
 constexpr int kNumBars = 16;
-constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+// shared-memory map for a Q/K head width of kDqk (a multiple of 64): Q | K x 2 | V x 2 | barriers
+template <int kDqk>
+struct Smem {
+    static constexpr int kSlabs = kDqk / 64;
+    static constexpr int kQBytes = kSlabs * kSlabBytes;   // 48 KB at 192
+    static constexpr int kKBytes = kSlabs * kSlabBytes;
+    static constexpr int kQ = 0;
+    static constexpr int kK = kQBytes;
+    static constexpr int kV = kK + 2 * kKBytes;
+    static constexpr int kBar = kV + 2 * kVBytes;         // 208 KB at 192, 160 KB at 128
+    static constexpr int kBytes = kBar + kNumBars * 8 + 32 + 1024;
+};
 constexpr uint32_t kColC = 0, kColP = 256, kColO = 384;
 
 enum : int {
@@ -76,12 +82,16 @@ struct Params {
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qt;
 };
 
+template <int kDqk>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    using L = Smem<kDqk>;
+    constexpr int kSmemQ = L::kQ, kSmemK = L::kK, kSmemV = L::kV, kSmemBar = L::kBar;
+    constexpr int kQBytes = L::kQBytes, kKBytes = L::kKBytes, kSlabs = L::kSlabs;
     const uint32_t bar0 = base + kSmemBar;
     const uint32_t bar_q_full = bar0;
     auto bar_k_full = [&](int s) { return bar0 + 8 * (1 + s); };
@@ -115,7 +125,7 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     auto load_k = [&](int j) {
         const int s = j & 1;
         mbar_arrive_expect_tx(bar_k_full(s), kKBytes);
-        for (int d = 0; d < 3; ++d)
+        for (int d = 0; d < kSlabs; ++d)
             tma_load_4d(base + kSmemK + s * kKBytes + d * kSlabBytes, &tm_k, bar_k_full(s), d * 64, j * kBN, kvh, b);
     };
     auto load_v = [&](int j) {
@@ -143,7 +153,7 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
         mbar_arrive_expect_tx(bar_q_full, kQBytes);
-        for (int d = 0; d < 3; ++d)
+        for (int d = 0; d < kSlabs; ++d)
             tma_load_4d(base + kSmemQ + d * kSlabBytes, &tm_q, bar_q_full, d * 64, q0, h, b);
         load_k(0);
         load_v(0);
@@ -198,7 +208,7 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t c = tmem_base + kColC + (j & 1) * kBN;
             tc_mma_ss_lo<false>(c, q_lo, ka, hi, kIdescQK);
 #pragma unroll
-            for (int ks = 1; ks < 12; ++ks) {
+            for (int ks = 1; ks < kDqk / 16; ++ks) {
                 const uint32_t off = ((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4;
                 tc_mma_ss_lo<true>(c, q_lo + off, ka + off, hi, kIdescQK);
             }
@@ -422,18 +432,9 @@ static int encode_map(CUtensorMap* map, const void* basep, int B, int H, int S, 
     return encode_bf16_4d(map, basep, dims, strides, box);
 }
 
-static int launch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
-                  int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, cudaStream_t stream) {
-    if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
-    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Dqk <= 0 || Dv <= 0) return CLLO_E_BAD_ARG;
-    if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
-    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16)) return CLLO_E_BAD_ARG;
-    if (Dqk != kDqk || Dv != kDv) return CLLO_E_UNSUPPORTED;
-    DeviceInfo* di = nullptr;
-    int rc = current_device_info(&di);
-    if (rc != CLLO_OK) return rc;
-    if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
-
+template <int kDqk>
+static int launch_width(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
+                        int Sq, int Skv, int Hq, int Hkv, DeviceInfo* di, bool* attr_set, cudaStream_t stream) {
     Params p;
     p.lse = lse;
     p.scale_log2 = scale * kLog2e;
@@ -448,18 +449,38 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     const long long blocks = static_cast<long long>(B) * Hq * p.n_qt;
     if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
 
+    int rc;
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if ((rc = encode_map(&tm_q, q, B, Hq, Sq, kDqk)) != CLLO_OK) return rc;
     if ((rc = encode_map(&tm_k, k, B, Hkv, Skv, kDqk)) != CLLO_OK) return rc;
     if ((rc = encode_map(&tm_v, v, B, Hkv, Skv, kDv)) != CLLO_OK) return rc;
     if ((rc = encode_map(&tm_o, o, B, Hq, Sq, kDv)) != CLLO_OK) return rc;
-    if (!di->mla_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(mla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        di->mla_attr_set = true;
+    constexpr int smem = Smem<kDqk>::kBytes;
+    if (!*attr_set) {
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(mla_fwd_kernel<kDqk>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        *attr_set = true;
     }
-    mla_fwd_kernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
+    (void)di;
+    mla_fwd_kernel<kDqk><<<static_cast<unsigned>(blocks), kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
+}
+
+// Dqk = 192 with Dv = 128 (the MLA shape), or Dqk = Dv = 128 (the GQA forward's one-tile case).
+static int launch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
+                  int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, cudaStream_t stream) {
+    if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Dqk <= 0 || Dv <= 0) return CLLO_E_BAD_ARG;
+    if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16)) return CLLO_E_BAD_ARG;
+    if ((Dqk != 192 && Dqk != 128) || Dv != kDv) return CLLO_E_UNSUPPORTED;
+    DeviceInfo* di = nullptr;
+    int rc = current_device_info(&di);
+    if (rc != CLLO_OK) return rc;
+    if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
+    if (Dqk == 192)
+        return launch_width<192>(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, di, &di->mla_attr_set, stream);
+    return launch_width<128>(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, di, &di->one_tile_attr_set, stream);
 }
 
 }  // namespace mla
