@@ -7,7 +7,7 @@
 //        -Xlinker -rpath=$PWD/cuda_llm_ops_b200 -o build/bench_flash_gqa
 //   ./build/bench_flash_gqa [B S Hq Hkv iters]
 //
-// Correctness is not judged here (the parity tests do that against the CPU oracle); inputs are a fixed pattern.
+// Correctness is not checked here (the parity tests do that against the CPU oracle); inputs are a fixed pattern.
 #include "cuda_llm_ops.h"
 
 #include <cuda_runtime.h>
