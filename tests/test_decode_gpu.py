@@ -185,6 +185,35 @@ def test_headline_shape_sampled_units_and_split_invariance():
     assert_clean_status()
 
 
+def test_long_context_shape_at_full_size():
+    """Baseline config 4 (one sequence, S=1,048,576, Hq=64, Hkv=8, inputs 0.5*N(0,1)) at full size: K and V hold
+    2^30 elements each.  The whole output is compared with the oracle, and the partials of two unequal position
+    ranges must combine to the same result."""
+    import cuda_llm_ops_b200 as ops
+    S, Hq, Hkv = 1 << 20, 64, 8
+    g = torch.Generator(device="cuda").manual_seed(77)
+    q = (0.5 * torch.randn((1, Hq, 128), generator=g, device="cuda")).to(torch.bfloat16)
+    k = torch.empty((1, Hkv, S, 128), dtype=torch.bfloat16, device="cuda")
+    v = torch.empty((1, Hkv, S, 128), dtype=torch.bfloat16, device="cuda")
+    for h in range(Hkv):
+        k[0, h] = (0.5 * torch.randn((S, 128), generator=g, device="cuda")).to(torch.bfloat16)
+        v[0, h] = (0.5 * torch.randn((S, 128), generator=g, device="cuda")).to(torch.bfloat16)
+    out = ops.gqa_decode(q, k, v, scale=SCALE, kv_layout=1)
+    cut = 700_001
+    parts = torch.zeros((2, 1, Hq, 130), dtype=torch.float32, device="cuda")
+    ops.gqa_decode(q, k[:, :, :cut].contiguous(), v[:, :, :cut].contiguous(), scale=SCALE, kv_layout=1,
+                   partial_out=parts[0])
+    ops.gqa_decode(q, k[:, :, cut:].contiguous(), v[:, :, cut:].contiguous(), scale=SCALE, kv_layout=1,
+                   partial_out=parts[1])
+    merged = ops.gqa_combine(parts)
+    torch.cuda.synchronize()
+    assert_clean_status()
+    got = to_bits(out)
+    want = ol.decode(to_bits(q), to_bits(k), to_bits(v), SCALE, 1)
+    ol.assert_parity(got, want, "long context")
+    ol.assert_parity(to_bits(merged), want, "long context, two position ranges")
+
+
 def test_exchange_kernel_with_a_world_of_one():
     """The peer exchange+combine kernel with world = 1 (its own buffers as the only peer): must equal the plain
     normalisation of the local partial, call after call (epoch 0 = count launches on the device)."""

@@ -107,3 +107,30 @@ def test_headline_prefill_shape_sampled_rows():
             ol.assert_parity(got[:, :, r0:r0 + 32], want_o[:, :, r0:r0 + 32], "rows %d causal=%d" % (r0, causal))
             assert np.allclose(lse.cpu().numpy()[:, :, r0:r0 + 32], want_lse[:, :, r0:r0 + 32], atol=LSE_TOL)
     assert_clean_status()
+
+
+def test_long_causal_shape_at_full_size_sampled_rows():
+    """Baseline config 5 (B=8, S=16384, Hq=64, Hkv=8, causal) whole on one GPU: Q and O are 2 GiB each, so the last
+    sequence sits beyond the reach of 32-bit byte offsets.  Sampled row windows of the first and last sequence (the
+    first rows, a 128-row tile boundary, the middle, the last rows) are checked against the oracle."""
+    import cuda_llm_ops_b200 as ops
+    B, Hq, Hkv, S = 8, 64, 8, 16384
+    g = torch.Generator(device="cuda").manual_seed(555)
+    q = torch.empty((B, Hq, S, 128), dtype=torch.bfloat16, device="cuda")
+    k = torch.empty((B, Hkv, S, 128), dtype=torch.bfloat16, device="cuda")
+    v = torch.empty((B, Hkv, S, 128), dtype=torch.bfloat16, device="cuda")
+    for b in range(B):   # one sequence at a time keeps the fp32 temporaries small
+        q[b] = torch.randn((Hq, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+        k[b] = torch.randn((Hkv, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+        v[b] = torch.randn((Hkv, S, 128), generator=g, device="cuda").to(torch.bfloat16)
+    out, lse = ops.launch_flash_gqa_forward_bf16_kernel(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    assert_clean_status()
+    for b in (0, B - 1):
+        qb, kb, vb = to_bits(q[b:b + 1]), to_bits(k[b:b + 1]), to_bits(v[b:b + 1])
+        for r0 in (0, 124, 8188, S - 8):
+            want_o, want_lse = ol.prefill(qb, kb, vb, SCALE, True, row_begin=r0, row_end=r0 + 8)
+            got_o = to_bits(out[b:b + 1, :, r0:r0 + 8].contiguous())
+            got_lse = lse[b:b + 1, :, r0:r0 + 8].cpu().numpy()
+            ol.assert_parity(got_o, want_o[:, :, r0:r0 + 8], "sequence %d rows %d" % (b, r0))
+            assert np.allclose(got_lse, want_lse[:, :, r0:r0 + 8], atol=LSE_TOL)
