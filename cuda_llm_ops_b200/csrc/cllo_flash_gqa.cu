@@ -197,10 +197,9 @@ int cllo_rope_bf16(const void* input, void* output, int B, int S, int hidden, fl
 }
 
 size_t cllo_gqa_bwd_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv) {
-    int sm = 1;  // no device visible: size for the finest head split
+    int sm = 1 << 20;  // no device visible: size for the finest head split
     DeviceInfo* di = nullptr;
     if (current_device_info(&di) == CLLO_OK && di->sm_count > 0) sm = di->sm_count;
-    else sm = 1 << 20;
     return backward::workspace_bytes(B, Sq, Skv, Hq, Hkv, sm);
 }
 
