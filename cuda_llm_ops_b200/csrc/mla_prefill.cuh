@@ -31,6 +31,8 @@ using prefill::kIdescQK;
 using prefill::kLn2;
 using prefill::kLog2e;
 using prefill::kRescaleThreshold;
+using prefill::max3;
+using prefill::min3;
 using prefill::pk2;
 using prefill::smem_desc_hi;
 using prefill::smem_desc_lo;
@@ -315,12 +317,22 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (c > limit) x[c] = masked;
             }
             float e0 = neg ? INFINITY : -INFINITY, e1 = e0, e2 = e0, e3 = e0;
+            if (neg) {
 #pragma unroll
-            for (int c = 0; c < 128; c += 4) {
-                e0 = neg ? fminf(e0, x[c]) : fmaxf(e0, x[c]);
-                e1 = neg ? fminf(e1, x[c + 1]) : fmaxf(e1, x[c + 1]);
-                e2 = neg ? fminf(e2, x[c + 2]) : fmaxf(e2, x[c + 2]);
-                e3 = neg ? fminf(e3, x[c + 3]) : fmaxf(e3, x[c + 3]);
+                for (int c = 0; c < 128; c += 8) {
+                    e0 = min3(e0, x[c], x[c + 1]);
+                    e1 = min3(e1, x[c + 2], x[c + 3]);
+                    e2 = min3(e2, x[c + 4], x[c + 5]);
+                    e3 = min3(e3, x[c + 6], x[c + 7]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 128; c += 8) {
+                    e0 = max3(e0, x[c], x[c + 1]);
+                    e1 = max3(e1, x[c + 2], x[c + 3]);
+                    e2 = max3(e2, x[c + 4], x[c + 5]);
+                    e3 = max3(e3, x[c + 6], x[c + 7]);
+                }
             }
             e0 = neg ? fminf(e0, e1) : fmaxf(e0, e1);
             e2 = neg ? fminf(e2, e3) : fmaxf(e2, e3);
