@@ -14,6 +14,9 @@
 // Shared memory: Q 48 KB (three [128][64] slabs, 128-byte swizzle), K 2 x 48 KB, V 2 x 32 KB.
 // The kernel is a template on the Q/K head width; the 128-wide instance serves the GQA forward when all query rows fit
 // one tile (Sq <= 128: decode-like chunks), where the two-tile kernel would spend half its work on an empty tile.
+// Query chunks of at most 64 rows go further: the heads of a group read the same K/V, so 128 / rows of them share the
+// tile (the Q and O tensor maps take a box of rows x heads, whose dense image in shared memory is the same [128][64]
+// slab; a thread's row maps to (head, query row) by a shift and a mask).
 // Warps: 0-3 softmax (one query row per thread), 4 TMA producer, 5 MMA issuer, 6-7 idle.  Barrier conventions,
 // bounded waits and the status word are those of the GQA forward kernel; so are the lazy rescaling, the packed
 // fp32 arithmetic and the bulk-store epilogue.
@@ -82,6 +85,8 @@ struct Params {
     float* lse;  // nullable
     float scale_log2;
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qt;
+    // short query chunks of a group share a tile: the 128 rows are `pack` heads x 2^row_shift query rows (1 x 128 otherwise)
+    int pack, row_shift, packs_per_group;
 };
 
 template <int kDqk>
@@ -110,14 +115,15 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // block -> (batch, kv head, query tile, head in group); heads of one group are neighbours so that they stream
     // the same K/V tiles through L2 together; heavy (late) causal tiles go first
     long long id = blockIdx.x;
-    const int g = static_cast<int>(id % p.G);
-    id /= p.G;
+    const int g = static_cast<int>(id % p.packs_per_group);
+    id /= p.packs_per_group;
     const int qt = p.n_qt - 1 - static_cast<int>(id % p.n_qt);
     id /= p.n_qt;
     const int kvh = static_cast<int>(id % p.Hkv);
     const int b = static_cast<int>(id / p.Hkv);
-    const int h = kvh * p.G + g;
+    const int h = kvh * p.G + g * p.pack;  // first (or only) head of the tile
     const int q0 = qt * kBM;
+    const int rows_used = p.pack << p.row_shift;  // 128 unless a small group leaves part of a packed tile empty
     int n_kv = (p.Skv + kBN - 1) / kBN;
     if (p.causal) {
         const int lim = (q0 + kBM - 1) / kBN + 1;
@@ -154,7 +160,7 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
-        mbar_arrive_expect_tx(bar_q_full, kQBytes);
+        mbar_arrive_expect_tx(bar_q_full, static_cast<uint32_t>(kSlabs * rows_used * 128));
         for (int d = 0; d < kSlabs; ++d)
             tma_load_4d(base + kSmemQ + d * kSlabBytes, &tm_q, bar_q_full, d * 64, q0, h, b);
         load_k(0);
@@ -164,6 +170,16 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (warp == 5) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
+    }
+    if (warp < 4 && static_cast<int>(threadIdx.x) >= rows_used) {
+        // rows of the Q tile that the copy does not fill: zeros, so that their scores stay finite
+        for (int d = 0; d < kSlabs; ++d)
+            for (int c = 0; c < 8; ++c)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + kSmemQ + d * kSlabBytes +
+                                                                                static_cast<int>(threadIdx.x) * 128 + c * 16),
+                             "r"(0)
+                             : "memory");
+        fence_async_proxy();
     }
     tc_fence_before();
     __syncthreads();
@@ -283,7 +299,8 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     } else if (warp < 4) {
         // ------------------------- softmax + epilogue (one row per thread) -------------------------
         const int row_in_tile = warp * 32 + lane;
-        const int qi = q0 + row_in_tile;
+        const int qi = q0 + (row_in_tile & ((1 << p.row_shift) - 1));
+        const int h_row = h + (row_in_tile >> p.row_shift);
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         const uint32_t o_addr = tmem_base + lane_base + kColO;
         float m = -INFINITY, l = 0.f;
@@ -423,8 +440,8 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tma_store_4d(&tm_o, stage_o + kSlabBytes, 64, q0, h, b);
             tma_store_commit_and_wait();
         }
-        if (qi < p.Sq && p.lse)
-            p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] = visible ? (m + log2f(l)) * kLn2 : -INFINITY;
+        if (qi < p.Sq && row_in_tile < rows_used && p.lse)
+            p.lse[(static_cast<long long>(b) * p.Hq + h_row) * p.Sq + qi] = visible ? (m + log2f(l)) * kLn2 : -INFINITY;
         tc_fence_before();
     }
 
@@ -435,12 +452,13 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
 }
 
-static int encode_map(CUtensorMap* map, const void* basep, int B, int H, int S, int D) {
+static int encode_map(CUtensorMap* map, const void* basep, int B, int H, int S, int D, int box_rows = 128,
+                      int box_heads = 1) {
     const uint64_t row = static_cast<uint64_t>(D) * 2;
     const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(H),
                               static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row, row * S, row * S * H};
-    const uint32_t box[4] = {64, 128, 1, 1};
+    const uint32_t box[4] = {64, static_cast<uint32_t>(box_rows), static_cast<uint32_t>(box_heads), 1};
     return encode_bf16_4d(map, basep, dims, strides, box);
 }
 
@@ -458,15 +476,31 @@ static int launch_width(const void* q, const void* k, const void* v, float scale
     p.G = Hq / Hkv;
     p.causal = causal ? 1 : 0;
     p.n_qt = (Sq + kBM - 1) / kBM;
-    const long long blocks = static_cast<long long>(B) * Hq * p.n_qt;
+    // Query chunks of at most 64 rows: the heads of a group read the same K/V, so 128 / rows of them share one tile
+    // (rows rounded up to a power of two, heads to a power of two that divides the group).
+    p.pack = 1;
+    p.row_shift = 7;
+    if (Sq <= 64) {
+        int shift = 0;
+        while ((1 << shift) < Sq) ++shift;
+        int pack = 1;
+        while (pack * 2 <= (128 >> shift) && p.G % (pack * 2) == 0) pack *= 2;
+        if (pack > 1) {
+            p.pack = pack;
+            p.row_shift = shift;
+        }
+    }
+    p.packs_per_group = p.G / p.pack;
+    const int box_rows = 1 << p.row_shift;
+    const long long blocks = static_cast<long long>(B) * Hkv * p.packs_per_group * p.n_qt;
     if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
 
     int rc;
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
-    if ((rc = encode_map(&tm_q, q, B, Hq, Sq, kDqk)) != CLLO_OK) return rc;
+    if ((rc = encode_map(&tm_q, q, B, Hq, Sq, kDqk, box_rows, p.pack)) != CLLO_OK) return rc;
     if ((rc = encode_map(&tm_k, k, B, Hkv, Skv, kDqk)) != CLLO_OK) return rc;
     if ((rc = encode_map(&tm_v, v, B, Hkv, Skv, kDv)) != CLLO_OK) return rc;
-    if ((rc = encode_map(&tm_o, o, B, Hq, Sq, kDv)) != CLLO_OK) return rc;
+    if ((rc = encode_map(&tm_o, o, B, Hq, Sq, kDv, box_rows, p.pack)) != CLLO_OK) return rc;
     constexpr int smem = Smem<kDqk>::kBytes;
     if (!*attr_set) {
         CLLO_CUDA_TRY(cudaFuncSetAttribute(mla_fwd_kernel<kDqk>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

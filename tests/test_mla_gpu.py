@@ -44,6 +44,9 @@ CASES = [
     (1, 2, 1, 520, 300, False),
     (1, 8, 2, 200, 1000, False),
     (1, 2, 2, 450, 130, True),           # rows beyond the last key see every key
+    (2, 8, 2, 40, 300, False),           # short query chunk: 2 heads of a group x 64 rows share the tile
+    (1, 16, 1, 3, 200, True),            # 16 heads x 4 rows
+    (1, 16, 2, 16, 129, False),          # 8 heads x 16 rows
 ]
 
 

@@ -43,6 +43,14 @@ CASES = [
     (1, 3, 1, 70, 300),       # Sq != Skv
     (1, 16, 1, 640, 640),     # group 16, like the headline prefill config
     (1, 2, 1, 1024, 1024),
+    # query chunks of at most 64 rows: heads of a group share one tile
+    (2, 8, 2, 64, 500),       # 2 heads x 64 rows
+    (1, 16, 1, 16, 300),      # 8 heads x 16 rows
+    (1, 16, 1, 1, 700),       # 16 heads x 1 row: part of the tile stays empty
+    (1, 6, 1, 33, 257),       # group of 6: 2 heads x 64 rows, rows 33..63 of each head beyond the chunk
+    (2, 4, 2, 5, 130),        # group of 2: 2 heads x 8 rows
+    (1, 3, 1, 20, 200),       # odd group: no sharing
+    (3, 32, 2, 7, 129),       # 16 heads x 8 rows
 ]
 
 
