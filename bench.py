@@ -14,6 +14,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
     sgqa            sparse-index GQA forward, upstream's shape (S=32768, 16 query heads on one kv head, lists of 512)
     backward        GQA attention backward (dQ, dK, dV), causal, upstream's shape
     swa             sliding-window forward with sink (mask variant of the prefill kernel), upstream's shape
+    prefill_chunk   64 query tokens against 8192 cached keys (the one-tile kernel, heads of a group sharing a tile)
 
 A step is one pass of the hot path over one batch.  `value` is whole-job throughput with inputs
 resident in HBM; `e2e` is the same metric through the package's public launcher with HOST buffers
@@ -242,6 +243,26 @@ def run_ours(args, rank, world, local_rank):
                   "global_batch": B * world, "seq_len": S, "sharding": "batch (no collective)",
                   "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
         host_in = [q, k, v]
+    elif wl == "prefill_chunk":
+        # a chunk of 64 new query tokens against 8192 cached ones (chunked prefill / speculative decoding): the
+        # one-tile kernel, two heads of a group sharing each 128-row tile
+        B, Sq, Skv, Hq, Hkv = 8, 64, 8192, 32, 4
+        q, k, v = randn_bf16((B, Hq, Sq, 128)), randn_bf16((B, Hkv, Skv, 128)), randn_bf16((B, Hkv, Skv, 128))
+        out = torch.empty_like(q)
+        lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        inner = lambda: ops.launch_flash_gqa_forward_bf16_kernel(q, k, v, out=out, lse=lse, causal=False)  # noqa: E731
+        step_fn = lambda: (flush.zero_(), inner())  # noqa: E731
+        units_per_rank = 4.0 * B * Hq * Sq * Skv * 128
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "gqa_prefill_tflops", "TFLOP/s", 1e12, "tensor"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "prefill_chunk: GQA forward, non-causal, 64 query tokens against 8192 keys, B=8 per GPU, "
+                              "Hq=32, Hkv=4, D=128",
+                  "global_batch": B * world, "seq_len": Skv, "sharding": "batch (no collective)",
+                  "l2": "256 MB buffer rewritten between iterations (outside the per-step event brackets)"}
+        host_in = [q, k, v]
     elif wl == "sgqa":
         # upstream's sparse-index GQA benchmark shape (README: 3690 us / 37.2 TFLOPS on an RTX 5080 Laptop).  Lists as
         # in upstream's test: the 16 most recent tokens, then uniformly drawn earlier ones, padded with -1 while the
@@ -351,7 +372,7 @@ def run_ours(args, rank, world, local_rank):
     t_begin = time.time()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa", "mla"):
+    if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -449,7 +470,9 @@ def run_ours(args, rank, world, local_rank):
                           else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
                                 else ("sgqa_fwd_kernel (bound by gathering 512 B per list entry out of L2, mma.sync "
                                       "products; the tensor peak is quoted for scale only)" if wl == "sgqa"
-                                      else ("mla_fwd_kernel" if wl == "mla" else "prefill_fwd_kernel"))),
+                                      else ("mla_fwd_kernel" if wl == "mla" else
+                                            ("mla_fwd_kernel<128> (the one-tile kernel)" if wl == "prefill_chunk"
+                                             else "prefill_fwd_kernel")))),
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
@@ -560,7 +583,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla"])
+                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")
