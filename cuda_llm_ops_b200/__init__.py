@@ -14,6 +14,7 @@ from .flash_gqa import (  # noqa: F401
     device_status,
     gqa_combine,
     gqa_decode,
+    gqa_decode_sharded,
     launch_decode_flash_gqa_bf16_kernel,
     launch_flash_gqa_backward_bf16_kernel,
     launch_flash_gqa_forward_bf16_kernel,
@@ -21,6 +22,7 @@ from .flash_gqa import (  # noqa: F401
     launch_flash_sgqa_forward_bf16_kernel,
     launch_flash_swa_backward_bf16_kernel,
     launch_flash_swa_forward_bf16_kernel,
+    set_exchange_wait_limit,
 )
 from .sharded import (  # noqa: F401
     KVShardedDecoder,

@@ -31,7 +31,12 @@ _SIGNATURES = {
     "cllo_gqa_decode_bf16": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "cllo_gqa_combine_bf16": (_i, [_vp, _i, _vp, _ll, _i, _vp]),
     "cllo_gqa_exchange_combine_bf16": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _i, ctypes.c_uint, _vp,
-                                            _ll, _i, _vp]),
+                                            _i, _i, _i, _i, _vp]),
+    "cllo_gqa_decode_sharded_bf16": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i,
+                                          ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _i, ctypes.c_uint, _vp]),
+    "cllo_gqa_shard_gather_bytes": (_sz, [_i, _i, _i, _i]),
+    "cllo_gqa_shard_flag_bytes": (_sz, [_i]),
+    "cllo_set_exchange_wait_limit": (_i, [_ll]),
     "cllo_gqa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "cllo_gqa_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),

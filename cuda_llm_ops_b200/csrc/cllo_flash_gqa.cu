@@ -13,12 +13,12 @@
 
 using namespace cllo;
 
-// Scratch for cllo_gqa_decode_bf16_noalloc: room for the split-KV partials of up to
+// Scratch for cllo_gqa_decode_bf16_noalloc: room for the split-KV partials (and arrival counters) of up to
 // CLLO_NOALLOC_MAX_WORKERS persistent blocks.  It lives in the library image, so every GPU that loads
 // the library carries these ~2.5 MiB until the process exits.  Host code must never hand this NAME to
 // a kernel: on the host it is only a stand-in, the device address comes from cudaGetSymbolAddress.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[
-    static_cast<size_t>(CLLO_NOALLOC_MAX_WORKERS) * 2 * decode::kSlotFloats * sizeof(float)];
+    static_cast<size_t>(CLLO_NOALLOC_MAX_WORKERS) * (2 * decode::kSlotFloats * sizeof(float) + sizeof(unsigned))];
 static void* g_noalloc_ptr[kMaxDevices];  // device address of the array, looked up once per device
 static std::mutex g_noalloc_mutex;
 
@@ -60,8 +60,12 @@ int cllo_shutdown(void) {
     }
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     for (int d = 0; d < kMaxDevices; ++d) {
-        if (g_dev[d].legacy_ws) {
-            if (cudaSetDevice(d) == cudaSuccess) (void)cudaFree(g_dev[d].legacy_ws);
+        if (g_dev[d].legacy_ws || !g_dev[d].retired_ws.empty()) {
+            if (cudaSetDevice(d) == cudaSuccess) {
+                (void)cudaFree(g_dev[d].legacy_ws);
+                for (void* old : g_dev[d].retired_ws) (void)cudaFree(old);
+            }
+            g_dev[d].retired_ws.clear();
             g_dev[d].legacy_ws = nullptr;
             g_dev[d].legacy_ws_bytes = 0;
         }
@@ -103,9 +107,19 @@ int cllo_gqa_decode_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, 
     return CLLO_OK;
 }
 
-int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
-                         size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout,
-                         int num_workers, float* partial_out, void* stream) {
+// Tensor maps of the most recent K/V cache seen by this host thread: a decode loop calls with the same cache
+// step after step, and encoding two maps costs about as much host time as the launch itself.
+struct KvMapCache {
+    const void* k = nullptr;
+    const void* v = nullptr;
+    int B = 0, S = 0, Hkv = 0, layout = -1;
+    CUtensorMap tm_k, tm_v;
+};
+static thread_local KvMapCache t_kv_maps;
+
+static int decode_launch(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
+                         size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout, int num_workers,
+                         float* partial_out, const shard::Params* sp, cudaStream_t st) {
     if (!q || !k || !v || (!o && !partial_out)) return CLLO_E_BAD_ARG;
     if (kv_layout != CLLO_KV_BSHD && kv_layout != CLLO_KV_BHSD) return CLLO_E_BAD_ARG;
     if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || (o && !aligned_to(o, 16)) ||
@@ -128,41 +142,72 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
     p.scale_log2 = scale * decode::kLog2e;
     p.kv_layout = kv_layout;
 
-    CUtensorMap tm_k, tm_v;
-    rc = decode::encode_kv_map(&tm_k, k, B, S, Hkv, kv_layout);
-    if (rc != CLLO_OK) return rc;
-    rc = decode::encode_kv_map(&tm_v, v, B, S, Hkv, kv_layout);
-    if (rc != CLLO_OK) return rc;
+    KvMapCache& mc = t_kv_maps;
+    if (mc.k != k || mc.v != v || mc.B != B || mc.S != S || mc.Hkv != Hkv || mc.layout != kv_layout) {
+        mc.layout = -1;
+        rc = decode::encode_kv_map(&mc.tm_k, k, B, S, Hkv, kv_layout);
+        if (rc != CLLO_OK) return rc;
+        rc = decode::encode_kv_map(&mc.tm_v, v, B, S, Hkv, kv_layout);
+        if (rc != CLLO_OK) return rc;
+        mc.k = k;
+        mc.v = v;
+        mc.B = B;
+        mc.S = S;
+        mc.Hkv = Hkv;
+        mc.layout = kv_layout;
+    }
 
     if (!di->decode_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel,
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<true>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
         di->decode_attr_set = true;
     }
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    decode::decode_splitkv_kernel<<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(tm_k, tm_v, p);
-    CLLO_CUDA_TRY(cudaGetLastError());
-    if (plan.needs_merge) {
-        // launched with programmatic stream serialization: its blocks become resident while the main
-        // kernel drains and start the moment that grid has completed
-        cudaLaunchConfig_t cfg = {};
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (plan.many_pieces) {
-            cfg.gridDim = dim3(static_cast<unsigned>(plan.units * decode::kRows));
-            cfg.blockDim = dim3(8 * 32);
-            CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel<8, 1>, p));
-        } else {
-            cfg.gridDim = dim3(static_cast<unsigned>(plan.units));
-            cfg.blockDim = dim3(decode::kRows * 32);
-            CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode::decode_merge_kernel<1, decode::kRows>, p));
-        }
+    // arrival counters of the units that a worker boundary cuts
+    if (plan.needs_merge)
+        CLLO_CUDA_TRY(cudaMemsetAsync(static_cast<char*>(workspace) + plan.counter_offset, 0, plan.counter_bytes, st));
+    if (sp) {
+        decode::decode_splitkv_kernel<true><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p, *sp);
+    } else {
+        shard::Params none = {};
+        decode::decode_splitkv_kernel<false><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p, none);
     }
+    CLLO_CUDA_TRY(cudaGetLastError());
+    return CLLO_OK;
+}
+
+int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
+                         size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout,
+                         int num_workers, float* partial_out, void* stream) {
+    return decode_launch(q, k, v, scale, o, workspace, workspace_bytes, B, S, Hq, Hkv, D, kv_layout, num_workers,
+                         partial_out, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int cllo_gqa_decode_sharded_bf16(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
+                                 size_t workspace_bytes, int B, int S_local, int Hq, int Hkv, int D, int kv_layout,
+                                 int num_workers, void* const* peer_gather, void* const* peer_flags, int rank,
+                                 int world, unsigned epoch, void* stream) {
+    if (!o) return CLLO_E_BAD_ARG;
+    shard::Params sp;
+    int rc = exchange::fill_shard_params(&sp, peer_gather, peer_flags, rank, world, epoch, B, Hq, Hkv);
+    if (rc != CLLO_OK) return rc;
+    return decode_launch(q, k, v, scale, o, workspace, workspace_bytes, B, S_local, Hq, Hkv, D, kv_layout,
+                         num_workers, nullptr, &sp, static_cast<cudaStream_t>(stream));
+}
+
+size_t cllo_gqa_shard_gather_bytes(int world, int B, int Hq, int D) {
+    if (world < 1 || world > CLLO_MAX_PEERS || B <= 0 || Hq <= 0 || D != shard::kD) return 0;
+    return static_cast<size_t>(2) * world * B * Hq * shard::kPW * sizeof(float);
+}
+
+size_t cllo_gqa_shard_flag_bytes(int world) {
+    if (world < 1 || world > CLLO_MAX_PEERS) return 0;
+    return (static_cast<size_t>(world) * shard::kMaxUnits + 1) * sizeof(unsigned);
+}
+
+int cllo_set_exchange_wait_limit(long long sm_cycles) {
+    exchange::g_wait_limit.store(sm_cycles > 0 ? sm_cycles : kWaitLimitCycles);
     return CLLO_OK;
 }
 
@@ -177,8 +222,9 @@ int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long 
 }
 
 int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer_gather, void* const* peer_flags,
-                                   int rank, int world, unsigned epoch, void* o, long long rows, int D, void* stream) {
-    return exchange::launch(local_partial, peer_gather, peer_flags, rank, world, epoch, o, rows, D,
+                                   int rank, int world, unsigned epoch, void* o, int B, int Hq, int Hkv, int D,
+                                   void* stream) {
+    return exchange::launch(local_partial, peer_gather, peer_flags, rank, world, epoch, o, B, Hq, Hkv, D,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -284,10 +330,12 @@ int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, flo
     } else {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
         if (di->legacy_ws_bytes < plan.ws_bytes) {
-            if (di->legacy_ws) CLLO_CUDA_TRY(cudaFree(di->legacy_ws));
-            di->legacy_ws = nullptr;
-            di->legacy_ws_bytes = 0;
-            CLLO_CUDA_TRY(cudaMalloc(&di->legacy_ws, plan.ws_bytes));
+            // an outgrown buffer is kept until cllo_shutdown(): another host thread may be between its look-up
+            // and its launch on it
+            void* fresh = nullptr;
+            CLLO_CUDA_TRY(cudaMalloc(&fresh, plan.ws_bytes));
+            if (di->legacy_ws) di->retired_ws.push_back(di->legacy_ws);
+            di->legacy_ws = fresh;
             di->legacy_ws_bytes = plan.ws_bytes;
         }
         ws = di->legacy_ws;

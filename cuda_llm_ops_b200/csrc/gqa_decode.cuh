@@ -19,13 +19,21 @@
 // (log-sum-exp algebra, fixed summation order) and every warp writes its share of either the final
 // bf16 output (unit entirely inside this worker) or an fp32 partial (O, m, l) in the workspace.
 //
-// Second pass.  decode_merge_kernel visits every unit that was cut by a worker boundary and merges
-// its partials:  m* = max m_i,  O = sum e^(m_i-m*) O_i / sum e^(m_i-m*) l_i.
+// Second pass, inside the same kernel.  A unit that a worker boundary cut leaves one fp32 partial per worker;
+// every worker counts itself in on the unit's arrival counter (after a fence) and the LAST one to arrive merges
+// all pieces, always in worker order:  m* = max m_i,  O = sum e^(m_i-m*) O_i / sum e^(m_i-m*) l_i.
+// No block ever waits for another one, so any number of workers is safe, and there is no second launch.
+//
+// Position-sharded mode (kSharded): the KV range of this call is one GPU's share of a longer sequence.  The block
+// that holds a unit's merged rows publishes them to every peer GPU and merges the peers' rows of the same unit
+// (gqa_shard.cuh), so the exchange of the early units overlaps the decode of the late ones and a whole step of a
+// sharded decode is this one kernel.
 //
 // HBM traffic per launch = K + V once (+ Q, O, and ~1% for partials): the algorithmic minimum.
 #pragma once
 
 #include "common.cuh"
+#include "gqa_shard.cuh"
 #include "host_util.cuh"
 
 namespace cllo {
@@ -60,7 +68,7 @@ struct Params {
     const __nv_bfloat16* q;
     __nv_bfloat16* o;
     float* partial_out;  // nullable
-    float* ws;           // [W][2][16][D+2]
+    float* ws;           // [W][2][16][D+2] partial slots, then [W] uint32 arrival counters (zero at kernel start)
     float scale_log2;    // scale * log2(e)
     int B, S, Hq, Hkv, G, n_gblk, n_t, kv_layout, W;
     long long T;  // total tiles
@@ -74,9 +82,10 @@ __host__ __device__ __forceinline__ long long worker_of_tile(long long t, long l
     return ((t + 1) * W - 1) / T;
 }
 
+template <bool kSharded>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const Params p) {
+                      const Params p, const shard::Params sp) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -85,6 +94,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     float* xchg = reinterpret_cast<float*>(gen_base + kSmemXchg);
     const uint32_t bar_base = base + kSmemBar;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + 2 * kStages * 8);
+    volatile int* misc = abort_flag + 1;  // [0] this block merges the unit, [1] step number (sharded mode)
     auto full_bar = [&](int s) { return bar_base + s * 8; };
     auto empty_bar = [&](int s) { return bar_base + (kStages + s) * 8; };
 
@@ -101,8 +111,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         fence_mbar_init();
     }
     __syncthreads();
-    // the merge pass may become resident now; it waits for this whole grid before it reads anything
-    pdl_launch_dependents();
     if (lo >= hi) return;
 
     if (warp == kConsumerWarps) {
@@ -349,14 +357,15 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
 
         // ---- every warp writes its share ----
+        const bool whole = (seg_lo == unit_lo) && (seg_hi == unit_hi);
+        const bool direct = whole && !kSharded;  // nothing else to merge with: straight to the output
         {
             const int hrow = warp & 1;             // 0: row g, 1: row g + 8
             const int row = g + 8 * hrow;
             const float mrow = hrow ? ms1 : ms0;
             const float lrow = hrow ? lt1 : lt0;
-            const bool whole = (seg_lo == unit_lo) && (seg_hi == unit_hi);
             if (row < rows) {
-                if (whole && p.partial_out == nullptr) {
+                if (direct && p.partial_out == nullptr) {
                     const float inv = 1.f / lrow;
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
@@ -366,7 +375,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                     }
                 } else {
                     float* dst;
-                    if (whole) {
+                    if (direct) {
                         dst = p.partial_out + (head0 + row) * kPW;
                     } else {
                         const int which = (u == u_first) ? 0 : 1;
@@ -384,98 +393,40 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 }
             }
         }
-    }
-}
+        if (direct) continue;
 
-// Second pass over the units that a worker boundary cut.  A block covers RB query-head rows of one unit
-// with PL piece-lanes x RB rows x 32 dim-lanes (4 dims each) threads.  Two shapes are used:
-//   <1,16>: many units cut in two or three pieces (a batch of sequences): one block per unit, no
-//           shared-memory step;
-//   <8,1> : few units cut into many pieces (one long sequence spread over all SMs): one block per row,
-//           pieces merged eight at a time, so the cost is a few load latencies instead of one per piece.
-template <int PL, int RB>
-__global__ void __launch_bounds__(PL * RB * 32) decode_merge_kernel(const Params p) {
-    constexpr int kBlocksPerUnit = kRows / RB;
-    const long long u = blockIdx.x / kBlocksPerUnit;
-    const long long t_first = u * p.n_t, t_last = t_first + p.n_t - 1;
-    const long long w_lo = worker_of_tile(t_first, p.T, p.W), w_hi = worker_of_tile(t_last, p.T, p.W);
-    if (w_lo == w_hi) return;  // the unit lived inside one worker, which wrote the final result
-    const int gblk = static_cast<int>(u % p.n_gblk);
-    const int kvh = static_cast<int>((u / p.n_gblk) % p.Hkv);
-    const int b = static_cast<int>(u / (static_cast<long long>(p.n_gblk) * p.Hkv));
-    const int rows = (p.G - gblk * kRows) < kRows ? (p.G - gblk * kRows) : kRows;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c4 = lane * 4;
-    const int pg = warp / RB;
-    const int r = static_cast<int>(blockIdx.x % kBlocksPerUnit) * RB + warp % RB;
-    if (r >= rows) return;  // with PL > 1 a block holds one row, so this exit is taken by whole blocks
-    const long long head0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * p.G + gblk * kRows;
-    const int which_lo = (worker_lo(w_lo, p.T, p.W) == t_first) ? 0 : 1;
-    __shared__ float s_max[PL];
-    __shared__ float s_l[PL];
-    __shared__ float4 s_acc[PL][32];
-    static_assert(PL == 1 || RB == 1, "the shared-memory reduction assumes one row per block");
-    pdl_wait_prior_grid();
-    auto row_ptr = [&](long long w) {
-        return p.ws + (w * 2 + (w == w_lo ? which_lo : 0)) * kSlotFloats + r * kPW;
-    };
-    // branch-free bodies so that the loads of several pieces are in flight together
-    float mstar = -INFINITY;
-#pragma unroll 4
-    for (long long w = w_lo + pg; w <= w_hi; w += PL) {
-        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(w) + kD);
-        mstar = fmaxf(mstar, ml.y > 0.f ? ml.x : -INFINITY);
-    }
-    if constexpr (PL > 1) {
-        if (lane == 0) s_max[pg] = mstar;
-        __syncthreads();
-        mstar = s_max[0];
-#pragma unroll
-        for (int i = 1; i < PL; ++i) mstar = fmaxf(mstar, s_max[i]);
-    }
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
-#pragma unroll 4
-    for (long long w = w_lo + pg; w <= w_hi; w += PL) {
-        const float* row = row_ptr(w);
-        const float2 ml = *reinterpret_cast<const float2*>(row + kD);
-        const float wgt = ml.y > 0.f ? __expf(ml.x - mstar) : 0.f;
-        const float2 x = *reinterpret_cast<const float2*>(row + c4);
-        const float2 y = *reinterpret_cast<const float2*>(row + c4 + 2);
-        a0 += wgt * x.x;
-        a1 += wgt * x.y;
-        a2 += wgt * y.x;
-        a3 += wgt * y.y;
-        lsum += wgt * ml.y;
-    }
-    if constexpr (PL > 1) {
-        s_acc[pg][lane] = make_float4(a0, a1, a2, a3);
-        if (lane == 0) s_l[pg] = lsum;
-        __syncthreads();
-        if (pg != 0) return;
-        lsum = s_l[0];
-#pragma unroll
-        for (int i = 1; i < PL; ++i) {  // fixed order: deterministic
-            const float4 t = s_acc[i][lane];
-            a0 += t.x;
-            a1 += t.y;
-            a2 += t.z;
-            a3 += t.w;
-            lsum += s_l[i];
+        // ---- this worker's piece of the unit is in the workspace: count it in; the last one to arrive merges ----
+        const long long w_first = worker_of_tile(unit_lo, p.T, p.W), w_last = worker_of_tile(unit_hi - 1, p.T, p.W);
+        const int n_pieces = static_cast<int>(w_last - w_first) + 1;
+        __threadfence();
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (threadIdx.x == 0) {
+            unsigned* counters = reinterpret_cast<unsigned*>(p.ws + static_cast<size_t>(p.W) * 2 * kSlotFloats);
+            const bool last = n_pieces == 1 || atomicAdd(counters + w_first, 1u) == static_cast<unsigned>(n_pieces - 1);
+            misc[0] = last ? 1 : 0;
+            if (kSharded && last) misc[1] = static_cast<int>(shard::take_epoch(sp));  // one ticket per unit
         }
-    }
-    if (p.partial_out) {
-        float* dst = p.partial_out + (head0 + r) * kPW;
-        *reinterpret_cast<float2*>(dst + c4) = make_float2(a0, a1);
-        *reinterpret_cast<float2*>(dst + c4 + 2) = make_float2(a2, a3);
-        if (c4 == 0) {
-            dst[kD] = mstar;
-            dst[kD + 1] = lsum;
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (misc[0] == 0) continue;
+        __threadfence();
+        {
+            const int tid = threadIdx.x, mrow_i = tid >> 4, c8 = (tid & 15) * 8;
+            const int which_first = (worker_lo(w_first, p.T, p.W) == unit_lo) ? 0 : 1;
+            float mg[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, mm = -INFINITY, ll = 0.f;
+            if (mrow_i < rows) {
+                shard::merge_rows(n_pieces, c8, [&](int i) {
+                    return p.ws + ((w_first + i) * 2 + (i == 0 ? which_first : 0)) * kSlotFloats + mrow_i * kPW;
+                }, mg, mm, ll);
+            }
+            if (kSharded) {
+                shard::publish_wait_combine(sp, static_cast<unsigned>(misc[1]), 1, tid, u, head0, rows, mg, mm, ll, p.o);
+            } else if (mrow_i < rows) {
+                if (p.partial_out)
+                    shard::store_packed_row(p.partial_out + (head0 + mrow_i) * kPW, c8, mg, mm, ll);
+                else
+                    shard::store_bf16_row(p.o + (head0 + mrow_i) * kD, c8, mg, ll);
+            }
         }
-    } else {
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        uint2 pk;
-        pk.x = pack_bf16x2(a0 * inv, a1 * inv);
-        pk.y = pack_bf16x2(a2 * inv, a3 * inv);
-        *reinterpret_cast<uint2*>(p.o + (head0 + r) * kD + c4) = pk;
     }
 }
 
@@ -505,9 +456,10 @@ __global__ void __launch_bounds__(kD) combine_rows_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------------
 struct Plan {
     Params prm;
-    size_t ws_bytes;
-    bool needs_merge;
-    bool many_pieces;  // some unit is cut into more than four pieces
+    size_t ws_bytes;        // partial slots + arrival counters
+    size_t counter_offset;  // byte offset of the counters inside the workspace
+    size_t counter_bytes;
+    bool needs_merge;       // some unit is cut by a worker boundary
     long long units;
 };
 
@@ -524,15 +476,16 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     p.n_gblk = (p.G + kRows - 1) / kRows;
     p.n_t = (S + kTok - 1) / kTok;
     plan->units = static_cast<long long>(B) * Hkv * p.n_gblk;
-    if (plan->units * kRows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // grid of the merge pass
+    if (plan->units * kRows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
     p.T = plan->units * p.n_t;
     long long W = num_workers > 0 ? num_workers : sm_count;
     if (W > p.T) W = p.T;
     if (W < 1) W = 1;
     p.W = static_cast<int>(W);
     if (p.T / W + 1 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // a worker's tile count is a 32-bit loop index
-    plan->ws_bytes = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
-    plan->many_pieces = (p.n_t / (p.T / W > 0 ? p.T / W : 1)) + 2 > 4;
+    plan->counter_offset = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
+    plan->counter_bytes = static_cast<size_t>(W) * sizeof(unsigned);
+    plan->ws_bytes = plan->counter_offset + plan->counter_bytes;
     plan->needs_merge = false;
     for (long long w = 1; w < W; ++w)
         if (worker_lo(w, p.T, W) % p.n_t != 0) {

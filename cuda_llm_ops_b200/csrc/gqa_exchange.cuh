@@ -1,145 +1,103 @@
-// All-gather of per-GPU decode partials + log-sum-exp combine in ONE kernel, over peer memory.
+// All-gather of per-GPU decode partials + log-sum-exp combine in ONE kernel, over peer memory: the exchange
+// protocol of gqa_shard.cuh driven from a packed partial that already sits in local memory.
 //
-// For a KV cache sharded by position across the GPUs of one NVSwitch domain, every rank holds a packed
-// partial (O, m, l) per query head of ITS positions (rows x (D+2) fp32, 33 KB at Hq=64).  This kernel
-//   1. stores the local partial into slot [rank] of every peer's gather buffer with plain peer stores
-//      (block p serves destination p), fences at system scope and publishes an epoch number in the
-//      peer's flag word for this rank;
-//   2. waits (bounded) until the flag words of all ranks in its OWN memory show the epoch;
-//   3. merges the `world` partials of its share of the rows and writes the bf16 output.
-// The exchange is a few tens of KB, so it is latency-bound: compared with a library all-gather followed
-// by a combine kernel it removes one collective launch and one kernel boundary from a ~100 us step.
-// Gather slots are double-buffered by epoch parity: a rank can be at most one call ahead of a peer,
-// because finishing call n needs that peer's flag of call n, which the peer raises only after its own
-// call n-1 has completed in stream order.
+// For a KV cache sharded by position across the GPUs of one NVSwitch domain, every rank holds a packed partial
+// (O, m, l) per query head of ITS positions (rows x (D+2) fp32, 33 KB at Hq=64).  One block per unit (batch, kv
+// head, block of <= 16 query heads) publishes that unit's rows to every peer, waits (bounded) for the peers' rows
+// of the same unit and writes the merged bf16 output.  The fused decode kernel (decode_splitkv_kernel<true>) does
+// the same from its registers as each unit finishes; this kernel serves ranks whose share of the sequence is empty
+// (they publish l = 0), callers that produced the partial some other way, and the protocol's tests.  Both speak
+// the same protocol, so ranks may mix them within one step.
 //
-// Every rank must launch this kernel for the same epoch; ranks live on different GPUs, so the kernels
-// that wait for one another always run concurrently.  No multicast objects, no TMA: ordinary loads and
-// stores to mapped peer memory.
+// Every rank must launch for the same step; ranks live on different GPUs, so the kernels that wait for one another
+// always run concurrently.
 #pragma once
 
+#include <atomic>
+
 #include "common.cuh"
+#include "gqa_shard.cuh"
 #include "host_util.cuh"
 
 namespace cllo {
 namespace exchange {
 
-constexpr int kD = 128;
-constexpr int kPW = kD + 2;
-constexpr int kThreads = 512;
+// How long a flag wait may take, in SM cycles; settable from the host (cllo_set_exchange_wait_limit).
+static std::atomic<long long> g_wait_limit{kWaitLimitCycles};
 
-struct Params {
-    const float* local;             // [rows][D+2]
-    float* gather[CLLO_MAX_PEERS];  // gather[p]: rank p's buffer [2][world][rows][D+2], mapped here
-    unsigned* flags[CLLO_MAX_PEERS];  // flags[p]: rank p's flag words [world]
-    __nv_bfloat16* o;               // [rows][D]
-    long long rows;
-    int rank, world;
-    unsigned epoch;
+struct Geometry {
+    int B, Hq, Hkv, G, n_gblk;
 };
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__global__ void __launch_bounds__(kThreads) exchange_combine_kernel(Params p) {
-    const int dst = blockIdx.x;  // destination rank served by this block; also its share of the rows in step 3
-    // epoch 0 = "count the calls on the device": every launch has exactly `world` blocks, each takes one
-    // ticket, so all blocks of the n-th launch derive n.  This keeps the call replayable from a CUDA graph.
+__global__ void __launch_bounds__(shard::kThreads) exchange_combine_kernel(const float* __restrict__ local,
+                                                                           __nv_bfloat16* o, Geometry geo,
+                                                                           const shard::Params sp) {
+    const long long u = blockIdx.x;
+    const int gblk = static_cast<int>(u % geo.n_gblk);
+    const int kvh = static_cast<int>((u / geo.n_gblk) % geo.Hkv);
+    const int b = static_cast<int>(u / (static_cast<long long>(geo.n_gblk) * geo.Hkv));
+    const int rows = (geo.G - gblk * shard::kRowsPerUnit) < shard::kRowsPerUnit ? (geo.G - gblk * shard::kRowsPerUnit)
+                                                                               : shard::kRowsPerUnit;
+    const long long head0 = static_cast<long long>(b) * geo.Hq + static_cast<long long>(kvh) * geo.G +
+                            gblk * shard::kRowsPerUnit;
     __shared__ unsigned s_epoch;
-    if (threadIdx.x == 0)
-        s_epoch = p.epoch ? p.epoch : atomicAdd(p.flags[p.rank] + p.world, 1u) / static_cast<unsigned>(p.world) + 1u;
+    if (threadIdx.x == 0) s_epoch = shard::take_epoch(sp);
     __syncthreads();
-    p.epoch = s_epoch;
-    const size_t slot_floats = static_cast<size_t>(p.rows) * kPW;
-    const size_t parity_off = static_cast<size_t>(p.epoch & 1u) * p.world * slot_floats;
-
-    // 1. push the local partial to peer `dst` (float2 granularity: rows are 520 bytes)
-    {
-        float2* out = reinterpret_cast<float2*>(p.gather[dst] + parity_off + static_cast<size_t>(p.rank) * slot_floats);
-        const float2* in = reinterpret_cast<const float2*>(p.local);
-        const size_t n2 = slot_floats / 2;
-        for (size_t i = threadIdx.x; i < n2; i += kThreads) out[i] = in[i];
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) st_release_sys(p.flags[dst] + p.rank, p.epoch);
-    }
-
-    // 2. wait for everybody's partial to have landed here
-    __shared__ int timed_out;
-    if (threadIdx.x == 0) timed_out = 0;
-    __syncthreads();
-    if (threadIdx.x < p.world) {
-        const unsigned* f = p.flags[p.rank] + threadIdx.x;
-        const long long t0 = clock64();
-        // epochs only grow; a later one would mean this call is being replayed out of step
-        while (static_cast<int>(ld_acquire_sys(f) - p.epoch) < 0) {
-            if (clock64() - t0 > kWaitLimitCycles) {
-                timed_out = 1;
-                record_timeout(SITE_EXCHANGE_FLAG, threadIdx.x);
-                break;
-            }
+    const int tid = threadIdx.x, row = tid >> 4, c8 = (tid & 15) * 8;
+    float val[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, m = -INFINITY, l = 0.f;
+    if (row < rows) {
+        const float* src = local + (head0 + row) * shard::kPW;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = *reinterpret_cast<const float2*>(src + c8 + 2 * e);
+            val[2 * e] = x.x;
+            val[2 * e + 1] = x.y;
         }
+        const float2 ml = *reinterpret_cast<const float2*>(src + shard::kD);
+        m = ml.x;
+        l = ml.y;
     }
-    __syncthreads();
-    if (timed_out) return;
+    shard::publish_wait_combine(sp, s_epoch, 1, tid, u, head0, rows, val, m, l, o);
+}
 
-    // 3. merge this block's share of the rows; thread = (row, 4 dims); data bypasses L1 (peers wrote it)
-    const float* mine = p.gather[p.rank] + parity_off;
-    const long long r_lo = p.rows * dst / p.world, r_hi = p.rows * (dst + 1) / p.world;
-    for (long long r = r_lo + (threadIdx.x >> 5); r < r_hi; r += kThreads / 32) {
-        const int c4 = (threadIdx.x & 31) * 4;
-        float mstar = -INFINITY;
-#pragma unroll 4
-        for (int s = 0; s < p.world; ++s) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(mine + s * slot_floats + r * kPW + kD));
-            mstar = fmaxf(mstar, ml.y > 0.f ? ml.x : -INFINITY);
-        }
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < p.world; ++s) {
-            const float* row = mine + s * slot_floats + r * kPW;
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(row + kD));
-            const float wgt = ml.y > 0.f ? __expf(ml.x - mstar) : 0.f;
-            const float2 x = __ldcg(reinterpret_cast<const float2*>(row + c4));
-            const float2 y = __ldcg(reinterpret_cast<const float2*>(row + c4 + 2));
-            a0 += wgt * x.x;
-            a1 += wgt * x.y;
-            a2 += wgt * y.x;
-            a3 += wgt * y.y;
-            lsum += wgt * ml.y;
-        }
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        uint2 pk;
-        pk.x = pack_bf16x2(a0 * inv, a1 * inv);
-        pk.y = pack_bf16x2(a2 * inv, a3 * inv);
-        *reinterpret_cast<uint2*>(p.o + r * kD + c4) = pk;
+// Fills the protocol parameters from the caller's pointer tables; shared with the fused decode launcher.
+static int fill_shard_params(shard::Params* sp, void* const* gather, void* const* flags, int rank, int world,
+                             unsigned epoch, int B, int Hq, int Hkv) {
+    if (!gather || !flags) return CLLO_E_BAD_ARG;
+    if (world < 1 || world > CLLO_MAX_PEERS || rank < 0 || rank >= world) return CLLO_E_BAD_ARG;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return CLLO_E_BAD_ARG;
+    const int G = Hq / Hkv;
+    const long long units = static_cast<long long>(B) * Hkv * ((G + shard::kRowsPerUnit - 1) / shard::kRowsPerUnit);
+    if (units > shard::kMaxUnits) return CLLO_E_UNSUPPORTED;
+    for (int i = 0; i < CLLO_MAX_PEERS; ++i) {
+        sp->gather[i] = i < world ? static_cast<float*>(gather[i]) : nullptr;
+        sp->flags[i] = i < world ? static_cast<unsigned*>(flags[i]) : nullptr;
+        if (i < world && (!sp->gather[i] || !sp->flags[i] || !aligned_to(sp->gather[i], 8) || !aligned_to(sp->flags[i], 4)))
+            return CLLO_E_BAD_ARG;
     }
+    sp->rows_total = static_cast<long long>(B) * Hq;
+    sp->wait_limit = g_wait_limit.load();
+    sp->rank = rank;
+    sp->world = world;
+    sp->units = static_cast<int>(units);
+    sp->epoch = epoch;
+    return CLLO_OK;
 }
 
 static int launch(const float* local, void* const* gather, void* const* flags, int rank, int world, unsigned epoch,
-                  void* o, long long rows, int D, cudaStream_t stream) {
-    if (!local || !gather || !flags || !o || rows <= 0) return CLLO_E_BAD_ARG;
-    if (world < 1 || world > CLLO_MAX_PEERS || rank < 0 || rank >= world) return CLLO_E_BAD_ARG;
-    if (D != kD) return CLLO_E_UNSUPPORTED;
-    Params p;
-    p.local = local;
-    for (int i = 0; i < CLLO_MAX_PEERS; ++i) {
-        p.gather[i] = i < world ? static_cast<float*>(gather[i]) : nullptr;
-        p.flags[i] = i < world ? static_cast<unsigned*>(flags[i]) : nullptr;
-        if (i < world && (!p.gather[i] || !p.flags[i] || !aligned_to(p.gather[i], 8))) return CLLO_E_BAD_ARG;
-    }
-    p.o = static_cast<__nv_bfloat16*>(o);
-    p.rows = rows;
-    p.rank = rank;
-    p.world = world;
-    p.epoch = epoch;
-    exchange_combine_kernel<<<world, kThreads, 0, stream>>>(p);
+                  void* o, int B, int Hq, int Hkv, int D, cudaStream_t stream) {
+    if (!local || !o || !aligned_to(local, 8) || !aligned_to(o, 16)) return CLLO_E_BAD_ARG;
+    if (D != shard::kD) return CLLO_E_UNSUPPORTED;
+    shard::Params sp;
+    int rc = fill_shard_params(&sp, gather, flags, rank, world, epoch, B, Hq, Hkv);
+    if (rc != CLLO_OK) return rc;
+    Geometry geo;
+    geo.B = B;
+    geo.Hq = Hq;
+    geo.Hkv = Hkv;
+    geo.G = Hq / Hkv;
+    geo.n_gblk = (geo.G + shard::kRowsPerUnit - 1) / shard::kRowsPerUnit;
+    exchange_combine_kernel<<<sp.units, shard::kThreads, 0, stream>>>(local, static_cast<__nv_bfloat16*>(o), geo, sp);
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }

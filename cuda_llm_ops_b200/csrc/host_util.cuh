@@ -4,7 +4,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -25,18 +27,21 @@ static thread_local int t_last_cuda_error = 0;
 constexpr int kMaxDevices = 64;
 
 struct DeviceInfo {
+    // the *_attr_set flags record that a kernel's launch attributes were set on this device; they are atomics
+    // because launchers on different host threads read and set them without taking g_dev_mutex
     bool valid = false;
     int sm_count = 0;
     int cc_major = 0;
     int cc_minor = 0;
-    bool decode_attr_set = false;
-    bool prefill_attr_set = false;
-    bool backward_attr_set = false;
-    bool sgqa_attr_set = false;
-    bool mla_attr_set = false;
-    bool one_tile_attr_set = false;
+    std::atomic<bool> decode_attr_set{false};
+    std::atomic<bool> prefill_attr_set{false};
+    std::atomic<bool> backward_attr_set{false};
+    std::atomic<bool> sgqa_attr_set{false};
+    std::atomic<bool> mla_attr_set{false};
+    std::atomic<bool> one_tile_attr_set{false};
     void* legacy_ws = nullptr;  // scratch cached by the source-compatibility wrapper only
     size_t legacy_ws_bytes = 0;
+    std::vector<void*> retired_ws;  // outgrown scratch buffers, freed by cllo_shutdown()
 };
 
 static DeviceInfo g_dev[kMaxDevices];

@@ -464,7 +464,7 @@ static int encode_map(CUtensorMap* map, const void* basep, int B, int H, int S, 
 
 template <int kDqk>
 static int launch_width(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
-                        int Sq, int Skv, int Hq, int Hkv, DeviceInfo* di, bool* attr_set, cudaStream_t stream) {
+                        int Sq, int Skv, int Hq, int Hkv, DeviceInfo* di, std::atomic<bool>* attr_set, cudaStream_t stream) {
     Params p;
     p.lse = lse;
     p.scale_log2 = scale * kLog2e;

@@ -57,12 +57,7 @@ def _require_cuda_bf16(name, t):
         raise ValueError("%s must be bf16" % name)
 
 
-def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=None, num_workers=0, workspace=None):
-    """Split-KV decode through ``cllo_gqa_decode_bf16``.
-
-    q [B,Hq,D]; k, v [B,S,Hkv,D] (KV_BSHD) or [B,Hkv,S,D] (KV_BHSD); returns out [B,Hq,D] bf16, or, when
-    ``partial_out`` ([B,Hq,D+2] fp32) is given, fills and returns that packed (O, m, l) tensor instead.
-    """
+def _decode_shapes(q, k, v, kv_layout):
     for name, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda_bf16(name, t)
     if q.dim() != 3 or k.dim() != 4 or v.shape != k.shape:
@@ -80,6 +75,16 @@ def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=Non
         raise ValueError("q, k and v must share batch and head_dim")
     if Hq % Hkv != 0:
         raise ValueError("Query heads must be divisible by KV heads")
+    return B, S, Hq, Hkv, D
+
+
+def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=None, num_workers=0, workspace=None):
+    """Split-KV decode through ``cllo_gqa_decode_bf16``.
+
+    q [B,Hq,D]; k, v [B,S,Hkv,D] (KV_BSHD) or [B,Hkv,S,D] (KV_BHSD); returns out [B,Hq,D] bf16, or, when
+    ``partial_out`` ([B,Hq,D+2] fp32) is given, fills and returns that packed (O, m, l) tensor instead.
+    """
+    B, S, Hq, Hkv, D = _decode_shapes(q, k, v, kv_layout)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     lib = _lib.load()
@@ -103,6 +108,38 @@ def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=Non
                                       B, S, Hq, Hkv, D, kv_layout, num_workers, p_ptr, _stream_ptr())
     _lib.check(rc, "cllo_gqa_decode_bf16")
     return result
+
+
+def gqa_decode_sharded(q, k_local, v_local, peer_gather, peer_flags, rank, world, epoch=0, scale=None,
+                       kv_layout=KV_BHSD, out=None, num_workers=0, workspace=None):
+    """One step of a KV-position-sharded decode in one kernel (``cllo_gqa_decode_sharded_bf16``).
+
+    ``k_local`` / ``v_local`` hold this rank's positions; ``peer_gather`` / ``peer_flags`` are ctypes arrays of
+    ``world`` device pointers (every rank's exchange buffers as mapped here).  Returns the full out [B,Hq,D] bf16,
+    identical on every rank.  Every rank must call once per step.
+    """
+    B, S, Hq, Hkv, D = _decode_shapes(q, k_local, v_local, kv_layout)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty_like(q)
+    if out.dtype != torch.bfloat16 or out.shape != q.shape or not out.is_contiguous():
+        raise ValueError("Output tensor must be contiguous bf16 of q's shape")
+    with torch.cuda.device(q.device):
+        nbytes = decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers)
+        if workspace is None:
+            workspace = _workspace(q.device, nbytes)
+        rc = _lib.load().cllo_gqa_decode_sharded_bf16(
+            q.data_ptr(), k_local.data_ptr(), v_local.data_ptr(), float(scale), out.data_ptr(),
+            workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, S, Hq, Hkv, D, kv_layout,
+            num_workers, peer_gather, peer_flags, rank, world, epoch, _stream_ptr())
+    _lib.check(rc, "cllo_gqa_decode_sharded_bf16")
+    return out
+
+
+def set_exchange_wait_limit(sm_cycles):
+    """Upper bound, in SM clock cycles, of one wait for a peer in the sharded decode (<= 0: the default, ~1 s)."""
+    _lib.check(_lib.load().cllo_set_exchange_wait_limit(int(sm_cycles)), "cllo_set_exchange_wait_limit")
 
 
 def gqa_combine(partials, out=None):

@@ -45,44 +45,55 @@ def shard_kv_positions(seq_len, world_size, rank, align=64):
 class _PeerBuffers:
     """Gather slots and flag words in memory that every rank of the node can address (torch symmetric memory).
 
-    Layout per rank: [2 parities][world][rows][D+2] fp32 gather slots, then `world` uint32 flag words and
-    one launch counter.
+    Layout per rank as ``include/cllo_flash_gqa.h`` describes it: [2 parities][world][rows][D+2] fp32 gather
+    slots, then [world][CLLO_SHARD_MAX_UNITS] uint32 flag words and one launch-ticket word, all zero at first.
     """
 
-    def __init__(self, group, rows, device):
+    def __init__(self, group, B, Hq, device):
         import torch.distributed._symmetric_memory as symm_mem
+        lib = _lib.load()
         self.world = dist.get_world_size(group)
-        self.rows = rows
-        n_gather = 2 * self.world * rows * flash_gqa.PARTIAL_WIDTH
-        self.storage = symm_mem.empty(n_gather + 64, dtype=torch.float32, device=device)
+        self.shape = (B, Hq)
+        gather_bytes = int(lib.cllo_gqa_shard_gather_bytes(self.world, B, Hq, flash_gqa.HEAD_DIM))
+        flag_bytes = int(lib.cllo_gqa_shard_flag_bytes(self.world))
+        if gather_bytes == 0 or flag_bytes == 0:
+            raise ValueError("unsupported world size or shape for the peer exchange")
+        self.storage = symm_mem.empty((gather_bytes + flag_bytes + 255) // 4, dtype=torch.float32, device=device)
         self.storage.zero_()
         handle = symm_mem.rendezvous(self.storage, group if group is not None else dist.group.WORLD)
         ptrs = [int(x) for x in handle.buffer_ptrs]
         self.handle = handle
         arr = ctypes.c_void_p * self.world
         self.gather_ptrs = arr(*ptrs)
-        self.flag_ptrs = arr(*[x + n_gather * 4 for x in ptrs])
-        self.epoch = 0
+        self.flag_ptrs = arr(*[x + gather_bytes for x in ptrs])
         torch.cuda.synchronize(device)
-        dist.barrier(group)  # every rank's flag words are zero before anybody publishes an epoch
+        dist.barrier(group)  # every rank's flag words are zero before anybody publishes a step
 
 
 class KVShardedDecoder:
     """Decode of sequences whose KV cache is sharded by position across the ranks of ``group``.
 
     ``exchange`` selects how the per-rank partials meet:
-      * ``"peer"``: one kernel (``cllo_gqa_exchange_combine_bf16``) stores the local partial into every
-        peer's memory, waits for the peers' flags and merges -- no library collective;
+      * ``"fused"``: ONE kernel per step (``cllo_gqa_decode_sharded_bf16``): the split-KV decode publishes each
+        head group's merged partial to every peer as soon as it is complete, waits for the peers' and writes the
+        final output -- no library collective, no second launch;
+      * ``"peer"``: decode into a local partial, then ``cllo_gqa_exchange_combine_bf16`` (same exchange protocol,
+        driven from memory);
       * ``"nccl"``: ``all_gather_into_tensor`` followed by the combine kernel (also the path CPU ranks take);
-      * ``"auto"``: ``"peer"`` when the ranks can map each other's memory, else ``"nccl"``.
+      * ``"auto"``: ``"fused"`` when the ranks can map each other's memory, else ``"nccl"``.
+
+    The peer forms wait for each other on the device with a bound (about a second; ``set_exchange_wait_limit``):
+    a rank that is later than that makes the others give up, their output rows become NaN and the device status
+    reports a time-out.  ``decode(..., check=True)`` reads that status (it synchronises the device) and raises.
+    The NCCL form simply waits.
 
     ``decode_fn(q, k, v, scale, kv_layout, partial_out)`` and ``combine_fn(partials) -> out`` default to the
     CUDA entry points; tests on CPU ranks (gloo) inject checker implementations to exercise the exchange.
     """
 
     def __init__(self, group=None, decode_fn=None, combine_fn=None, exchange="nccl"):
-        if exchange not in ("nccl", "peer", "auto"):
-            raise ValueError("exchange must be 'nccl', 'peer' or 'auto'")
+        if exchange not in ("nccl", "peer", "fused", "auto"):
+            raise ValueError("exchange must be 'nccl', 'peer', 'fused' or 'auto'")
         self.group = group
         self.world_size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -92,6 +103,7 @@ class KVShardedDecoder:
         self._exchange_request = exchange
         self.exchange = "nccl"  # what is actually in use; settled at the first decode on a device
         self._peer = None
+        self._peer_tried = False
         self._local = None
 
     @staticmethod
@@ -104,20 +116,21 @@ class KVShardedDecoder:
             self._gathered = torch.zeros(shape, dtype=torch.float32, device=device)
         return self._gathered
 
-    def _setup_peer(self, rows, device):
+    def _setup_peer(self, B, Hq, device):
         """Try to set up peer-addressable buffers; every rank must agree on the outcome."""
         ok = 1
         try:
-            peer = _PeerBuffers(self.group, rows, device)
-        except Exception as exc:  # symmetric memory unavailable (no P2P, old driver, ...)
-            if self._exchange_request == "peer":
+            peer = _PeerBuffers(self.group, B, Hq, device)
+        except Exception as exc:  # symmetric memory unavailable (no P2P, old driver, ...) or shape not supported
+            if self._exchange_request in ("peer", "fused"):
                 raise
             peer, ok = None, 0
             self._peer_error = repr(exc)
         flag = torch.tensor([ok], dtype=torch.int32, device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         if int(flag.item()) == 1:
-            self._peer, self.exchange = peer, "peer"
+            self._peer = peer
+            self.exchange = "peer" if self._exchange_request == "peer" else "fused"
         else:
             self._peer, self.exchange = None, "nccl"
 
@@ -133,15 +146,21 @@ class KVShardedDecoder:
             self._decode(q, k_local, v_local, scale, kv_layout, mine)
         return mine
 
-    def decode(self, q, k_local, v_local, scale=None, kv_layout=flash_gqa.KV_BHSD, out=None):
+    def decode(self, q, k_local, v_local, scale=None, kv_layout=flash_gqa.KV_BHSD, out=None, check=False):
         """q [B,Hq,D] replicated; k_local/v_local hold this rank's positions.  Returns the full O on every rank."""
         B, Hq, D = q.shape
         if self._exchange_request != "nccl" and q.is_cuda and self.world_size > 1:
-            if self._peer is None and self.exchange == "nccl" and not getattr(self, "_peer_tried", False):
+            if not self._peer_tried:
                 self._peer_tried = True
-                self._setup_peer(B * Hq, q.device)
-            if self._peer is not None and self._peer.rows == B * Hq:
-                return self._decode_peer(q, k_local, v_local, scale, kv_layout, out)
+                self._setup_peer(B, Hq, q.device)
+            if self._peer is not None and self._peer.shape == (B, Hq):
+                res = self._decode_peer(q, k_local, v_local, scale, kv_layout, out)
+                if check:
+                    rc, detail = flash_gqa.device_status()
+                    if rc != 0:
+                        raise RuntimeError("sharded decode: a peer did not deliver its partial in time "
+                                           "(device status %d, detail %s); the output holds NaN" % (rc, detail))
+                return res
         mine = self.local_partial(q, k_local, v_local, scale, kv_layout)
         gathered = self._gathered
         if self.world_size > 1:
@@ -156,16 +175,23 @@ class KVShardedDecoder:
 
     def _decode_peer(self, q, k_local, v_local, scale, kv_layout, out):
         B, Hq, D = q.shape
-        if self._local is None or tuple(self._local.shape) != (B, Hq, flash_gqa.PARTIAL_WIDTH):
-            self._local = torch.zeros((B, Hq, flash_gqa.PARTIAL_WIDTH), dtype=torch.float32, device=q.device)
-        self.local_partial(q, k_local, v_local, scale, kv_layout, out=self._local)
         if out is None:
             out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=q.device)
         peer = self._peer
+        s_axis = 1 if kv_layout == flash_gqa.KV_BSHD else 2
+        if self.exchange == "fused" and k_local.shape[s_axis] > 0:
+            # epoch 0: the kernels count their launches on the device, so a step can sit in a CUDA graph
+            flash_gqa.gqa_decode_sharded(q, k_local, v_local, peer.gather_ptrs, peer.flag_ptrs, self.rank,
+                                         self.world_size, epoch=0, scale=scale, kv_layout=kv_layout, out=out)
+            return out
+        # two launches: this rank's partial (an empty share gives l = 0 rows), then the exchange from memory
+        if self._local is None or tuple(self._local.shape) != (B, Hq, flash_gqa.PARTIAL_WIDTH):
+            self._local = torch.zeros((B, Hq, flash_gqa.PARTIAL_WIDTH), dtype=torch.float32, device=q.device)
+        self.local_partial(q, k_local, v_local, scale, kv_layout, out=self._local)
+        Hkv = k_local.shape[2] if kv_layout == flash_gqa.KV_BSHD else k_local.shape[1]
         with torch.cuda.device(q.device):
-            # epoch 0: the kernel counts its launches on the device, so this call can sit in a CUDA graph
             rc = _lib.load().cllo_gqa_exchange_combine_bf16(
                 self._local.data_ptr(), peer.gather_ptrs, peer.flag_ptrs, self.rank, self.world_size, 0,
-                out.data_ptr(), B * Hq, D, torch.cuda.current_stream().cuda_stream)
+                out.data_ptr(), B, Hq, Hkv, D, torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "cllo_gqa_exchange_combine_bf16")
         return out

@@ -43,7 +43,8 @@ int cllo_last_cuda_error(void);
  * library recorded a timed-out wait since the last call, and clears the record.  detail (host,
  * nullable) receives {code, block, site, aux}. */
 int cllo_device_status(int detail[4]);
-/* Frees the per-device scratch that LaunchFlashGqaBf16Kernel's compatibility path may have cached. */
+/* Frees the per-device scratch that LaunchFlashGqaBf16Kernel's compatibility path may have cached.  Call it
+ * when no launch of that path is in flight on any thread. */
 int cllo_shutdown(void);
 
 /*
@@ -57,10 +58,14 @@ int cllo_shutdown(void);
  *
  *   q [B,Hq,D]   k,v per kv_layout   o [B,Hq,D] bf16
  *   workspace / workspace_bytes: scratch of at least cllo_gqa_decode_workspace_bytes(...) bytes,
- *       256-byte aligned.  The KV range of every (batch, kv head) is cut into equal shares for
- *       `num_workers` persistent thread blocks; shares that cover only part of a head leave fp32
- *       partials (O, m, l) in the workspace and a second kernel merges them by log-sum-exp.
+ *       256-byte aligned, contents arbitrary.  The KV range of every (batch, kv head) is cut into equal
+ *       shares for `num_workers` persistent thread blocks; shares that cover only part of a head leave
+ *       fp32 partials (O, m, l) in the workspace, and the last block to finish a head's share merges them
+ *       by log-sum-exp (second pass, same kernel; the call zeroes its arrival counters with a memset node
+ *       on `stream` first).  Calls that may overlap on the GPU need a workspace each.
  *   num_workers: 0 = one per SM of the current device.
+ *   Group sizes above 16: the query heads of a group are served in blocks of 16 and each block streams the
+ *       group's K/V again, so G = 32 reads K/V twice (no upstream configuration has G > 16).
  *   partial_out (nullable): when given, `o` is ignored and the call writes, for every (b, h), one
  *       packed fp32 row [D+2] = {un-normalised O, m = max scaled score, l = sum exp(score - m)} of
  *       THIS call's KV range.  This is what a KV-position-sharded caller all-gathers and feeds to
@@ -73,8 +78,8 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
                          int kv_layout, int num_workers, float* partial_out, void* stream);
 
 /* How a decode call would be cut up: plan[0] = workers actually launched, plan[1] = KV tiles per
- * (batch, kv head, 16-query-head block), plan[2..3] = total tiles (low, high 32 bits), plan[4] = 1 if the
- * merge pass runs, plan[5] = tokens per tile.  Host-only arithmetic; sm_count <= 0 means "ask the device". */
+ * (batch, kv head, 16-query-head block), plan[2..3] = total tiles (low, high 32 bits), plan[4] = 1 if some
+ * head's share is cut between workers (partials are merged), plan[5] = tokens per tile.  Host-only arithmetic; sm_count <= 0 means "ask the device". */
 int cllo_gqa_decode_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int sm_count, int plan[6]);
 
 /* Upstream's launcher signature without a workspace argument (LaunchFlashGqaBf16Kernel,
@@ -99,12 +104,15 @@ int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, flo
  * Same arguments and results as cllo_gqa_decode_bf16 without workspace and partial_out.  Limits:
  *   - num_workers > CLLO_NOALLOC_MAX_WORKERS is refused with CLLO_E_WORKSPACE (the partials would not
  *     fit); num_workers == 0 uses min(SM count, CLLO_NOALLOC_MAX_WORKERS).  B, S and the head counts are
- *     not limited by the scratch: its size depends on the number of workers only.
+ *     not limited by the scratch: its size depends on the number of workers only.  On a GPU with more
+ *     than CLLO_NOALLOC_MAX_WORKERS SMs the default therefore leaves SMs idle and the call is slower than
+ *     cllo_gqa_decode_bf16 with a workspace.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *     device current) and remembers it; make that first call outside any stream capture.
- *   - All calls on one device share the one array and it keeps the previous call's contents.  Nothing
- *     in it has to start at zero (every partial the merge pass reads was written earlier in the same
- *     call), but two calls that overlap on the GPU (different streams) race on it: serialise them.
+ *   - All calls on one device share the one array and it keeps the previous call's contents.  The only
+ *     part that has to start at zero, the arrival counters, is cleared by a memset on `stream` at the
+ *     start of every call (every partial that is merged was written earlier in the same call); but two
+ *     calls that overlap on the GPU (different streams) race on the array: serialise them.
  */
 #define CLLO_NOALLOC_MAX_WORKERS 160
 int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, float scale, void* o,
@@ -121,25 +129,47 @@ int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, fl
 int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long rows, int D, void* stream);
 
 /*
- * Exchange + merge for one sequence whose KV cache is sharded by position over the GPUs of one node:
- * all-gather of every rank's packed partial and the log-sum-exp combine, in one kernel over peer memory
- * (plain peer stores and flag words; no library collective).  Upstream has no multi-GPU code; this
- * replaces "ncclAllGather + cllo_gqa_combine_bf16" when the ranks can map each other's memory.
+ * One sequence (or batch) whose KV cache is sharded by POSITION over the GPUs of one node.  Upstream has no
+ * multi-GPU code; these entry points are the exchange step such a caller needs, over peer memory (plain peer
+ * loads/stores and flag words; no library collective, no multicast).
  *
- *   local_partial [rows][D+2]: this rank's partial (the partial_out of cllo_gqa_decode_bf16).
- *   peer_gather, peer_flags: HOST arrays of `world` device pointers, entry p = rank p's gather buffer
- *       ([2][world][rows][D+2] fp32) and flag words ([world + 1] uint32, zeroed once before the first
- *       call), as mapped into THIS process (e.g. CUDA IPC / symmetric memory); entry `rank` is the local one.
- *   epoch: 1, 2, 3, ... the same on every rank for the same step; or 0 on every rank and every call, in
- *       which case the kernel counts its own launches in the extra flag word (a call sequence that never
- *       changes its arguments, e.g. one replayed from a CUDA graph).  Every rank must make the call; a
- *       rank that never does makes the others' bounded wait (about a second) expire, which is reported
- *       through cllo_device_status() with results left invalid.
- *   o [rows][D] bf16: the merged output, produced on every rank.
+ * Buffers, per rank, in memory that every rank has mapped (CUDA IPC, symmetric memory, ...), zeroed once before
+ * the first step:
+ *   gather  cllo_gqa_shard_gather_bytes(world, B, Hq, D) bytes: [2][world][B*Hq][D+2] fp32
+ *   flags   cllo_gqa_shard_flag_bytes(world) bytes: [world][CLLO_SHARD_MAX_UNITS] uint32 + one ticket word
+ * peer_gather / peer_flags are HOST arrays of `world` device pointers, entry p = rank p's buffer as mapped into
+ * THIS process; entry `rank` is the local one.  B * Hkv * ceil((Hq/Hkv)/16) must not exceed CLLO_SHARD_MAX_UNITS.
+ *
+ *   epoch: 1, 2, 3, ... the same on every rank for the same step; or 0 on every rank and every step, in which case
+ *       the kernels count their own launches in the ticket word (a call sequence that never changes its arguments,
+ *       e.g. one replayed from a CUDA graph).  Every rank must make one call per step.  A rank that is late by more
+ *       than the wait limit (about a second unless changed by cllo_set_exchange_wait_limit) makes the others' wait
+ *       expire: their output rows are filled with NaN and cllo_device_status() reports CLLO_E_DEVICE_TIMEOUT.
+ *
+ * cllo_gqa_decode_sharded_bf16: the whole step in one kernel.  Split-KV decode of this rank's S_local positions
+ *   (arguments as cllo_gqa_decode_bf16); as the last piece of each (batch, kv head) arrives, that head's merged
+ *   (O, m, l) rows are stored into every peer's gather buffer, the peers' rows are awaited and the final bf16
+ *   o [B,Hq,D] is written -- on every rank.  The exchange of early heads overlaps the decode of late ones.
+ * cllo_gqa_exchange_combine_bf16: the same exchange for a packed partial that already exists
+ *   (local_partial [B*Hq][D+2], e.g. partial_out of cllo_gqa_decode_bf16, or l = 0 rows from a rank whose share of
+ *   the sequence is empty).  Ranks may mix the two entry points within a step.
+ * cllo_set_exchange_wait_limit: upper bound of one flag wait in SM clock cycles (<= 0 restores the default);
+ *   applies to later launches of either entry point.
  */
 #define CLLO_MAX_PEERS 16
+#define CLLO_SHARD_MAX_UNITS 256
+size_t cllo_gqa_shard_gather_bytes(int world, int B, int Hq, int D);
+size_t cllo_gqa_shard_flag_bytes(int world);
+int cllo_set_exchange_wait_limit(long long sm_cycles);
+int cllo_gqa_decode_sharded_bf16(const void* q, const void* k, const void* v, float scale, void* o,
+                                 void* workspace, size_t workspace_bytes,
+                                 int B, int S_local, int Hq, int Hkv, int D,
+                                 int kv_layout, int num_workers,
+                                 void* const* peer_gather, void* const* peer_flags, int rank, int world,
+                                 unsigned epoch, void* stream);
 int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer_gather, void* const* peer_flags,
-                                   int rank, int world, unsigned epoch, void* o, long long rows, int D, void* stream);
+                                   int rank, int world, unsigned epoch, void* o,
+                                   int B, int Hq, int Hkv, int D, void* stream);
 
 /*
  * Multi-token (prefill) GQA forward:  O = softmax(mask(scale * Q K^T)) V,  lse = m + log(l).

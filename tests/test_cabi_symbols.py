@@ -47,10 +47,20 @@ def test_argument_validation_needs_no_gpu(built_library):
     # peer exchange: null tables, rank outside the world, epoch 0, too many peers
     two = (ctypes.c_void_p * 2)(1 << 20, 2 << 20)
     ex = lib.cllo_gqa_exchange_combine_bf16
-    assert ex(None, None, None, 0, 2, 1, None, 64, 128, None) == _lib.E_BAD_ARG
-    assert ex(1 << 20, two, two, 2, 2, 1, 1 << 20, 64, 128, None) == _lib.E_BAD_ARG
-    assert ex(1 << 20, two, two, 0, 17, 1, 1 << 20, 64, 128, None) == _lib.E_BAD_ARG
-    assert ex(1 << 20, two, two, 0, 2, 1, 1 << 20, 64, 64, None) == _lib.E_UNSUPPORTED
+    assert ex(None, None, None, 0, 2, 1, None, 1, 64, 8, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 2, 2, 1, 1 << 20, 1, 64, 8, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 0, 17, 1, 1 << 20, 1, 64, 8, 128, None) == _lib.E_BAD_ARG
+    assert ex(1 << 20, two, two, 0, 2, 1, 1 << 20, 1, 64, 8, 64, None) == _lib.E_UNSUPPORTED
+    assert ex(1 << 20, two, two, 0, 2, 1, 1 << 20, 1, 64, 6, 128, None) == _lib.E_BAD_ARG       # Hq % Hkv
+    assert ex(1 << 20, two, two, 0, 2, 1, 1 << 20, 300, 8, 8, 128, None) == _lib.E_UNSUPPORTED  # too many units
+    # the fused form validates the exchange tables before anything else
+    fused = lib.cllo_gqa_decode_sharded_bf16
+    assert fused(1 << 20, 1 << 20, 1 << 20, 1.0, 1 << 20, None, 0, 1, 64, 64, 8, 128, 0, 0, None, None, 0, 2, 1,
+                 None) == _lib.E_BAD_ARG
+    assert lib.cllo_gqa_shard_gather_bytes(8, 1, 64, 128) == 2 * 8 * 64 * 130 * 4
+    assert lib.cllo_gqa_shard_flag_bytes(8) == (8 * 256 + 1) * 4
+    assert lib.cllo_gqa_shard_flag_bytes(17) == 0
+    assert lib.cllo_set_exchange_wait_limit(0) == 0
 
 
 def test_decode_plan_balances_tiles(built_library):
@@ -69,7 +79,8 @@ def test_decode_plan_balances_tiles(built_library):
     assert lib.cllo_gqa_decode_plan(4, 1024, 32, 8, 128, 32, 148, plan) == 0 and plan[4] == 0
     assert lib.cllo_gqa_decode_plan(1, 64, 6, 4, 128, 0, 148, plan) == _lib.E_BAD_ARG
     assert lib.cllo_gqa_decode_plan(1, 64, 4, 4, 64, 0, 148, plan) == _lib.E_UNSUPPORTED
-    assert lib.cllo_gqa_decode_workspace_bytes(60, 4096, 128, 8, 128, 148) == 148 * 2 * 16 * 130 * 4
+    # partial slots plus one arrival counter per worker
+    assert lib.cllo_gqa_decode_workspace_bytes(60, 4096, 128, 8, 128, 148) == 148 * (2 * 16 * 130 * 4 + 4)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -35,6 +35,7 @@ CASES = [
     (2, 63, 40, 2),       # group 20 -> two 16-row blocks per kv head
     (1, 65, 16, 1),       # one token into the second tile
     (5, 200, 8, 1),
+    (2, 3000, 64, 2),     # group 32: two 16-row blocks per kv head, every block's share cut between workers
 ]
 
 
@@ -51,9 +52,9 @@ def test_parity_with_cpu_oracle(B, S, Hq, Hkv, layout):
     assert_clean_status()
 
 
-@pytest.mark.parametrize("workers", [1, 2, 3, 7, 31, 148, 296])
+@pytest.mark.parametrize("workers", [1, 2, 3, 7, 31, 148, 296, 1000])
 def test_result_does_not_depend_on_the_number_of_workers(workers):
-    B, S, Hq, Hkv = 2, 1000, 16, 2
+    B, S, Hq, Hkv = 2, 3000, 16, 2  # 188 tiles: the largest counts launch more blocks than the GPU has SMs
     q = ol.randn_bf16((B, Hq, 128), 21)
     k = ol.randn_bf16((B, S, Hkv, 128), 22)
     v = ol.randn_bf16((B, S, Hkv, 128), 23)
@@ -214,28 +215,97 @@ def test_long_context_shape_at_full_size():
     ol.assert_parity(to_bits(merged), want, "long context, two position ranges")
 
 
-def test_exchange_kernel_with_a_world_of_one():
-    """The peer exchange+combine kernel with world = 1 (its own buffers as the only peer): must equal the plain
-    normalisation of the local partial, call after call (epoch 0 = count launches on the device)."""
+def _exchange_buffers(world, B, Hq):
+    """One rank's gather slots + flag words (zeroed), as (tensor, gather pointer, flag pointer)."""
+    from cuda_llm_ops_b200 import _lib
+    lib = _lib.load()
+    gb, fb = int(lib.cllo_gqa_shard_gather_bytes(world, B, Hq, 128)), int(lib.cllo_gqa_shard_flag_bytes(world))
+    assert gb > 0 and fb > 0
+    buf = torch.zeros((gb + fb) // 4, dtype=torch.float32, device="cuda")
+    return buf, buf.data_ptr(), buf.data_ptr() + gb
+
+
+def test_exchange_kernels_with_a_world_of_one():
+    """Both forms of the peer exchange with world = 1 (their own buffers as the only peer): the fused decode and
+    the exchange from a stored partial must equal the plain decode, call after call (epoch 0 = the kernels count
+    their launches on the device)."""
     import ctypes
     import cuda_llm_ops_b200 as ops
     from cuda_llm_ops_b200 import _lib
-    B, S, Hq, Hkv = 1, 900, 16, 2
+    B, S, Hq, Hkv = 2, 900, 16, 2
     q = ol.randn_bf16((B, Hq, 128), 81)
     k = ol.randn_bf16((B, Hkv, S, 128), 82)
     v = ol.randn_bf16((B, Hkv, S, 128), 83)
+    qd, kd, vd = to_dev(q), to_dev(k), to_dev(v)
     part = torch.zeros((B, Hq, 130), dtype=torch.float32, device="cuda")
-    ops.gqa_decode(to_dev(q), to_dev(k), to_dev(v), scale=SCALE, kv_layout=1, partial_out=part)
-    rows = B * Hq
-    buf = torch.zeros(2 * 1 * rows * 130 + 64, dtype=torch.float32, device="cuda")
+    ops.gqa_decode(qd, kd, vd, scale=SCALE, kv_layout=1, partial_out=part)
+    buf, g_ptr, f_ptr = _exchange_buffers(1, B, Hq)
     arr = ctypes.c_void_p * 1
-    gather, flags = arr(buf.data_ptr()), arr(buf.data_ptr() + 2 * rows * 130 * 4)
+    gather, flags = arr(g_ptr), arr(f_ptr)
     want = ol.decode(q, k, v, SCALE, 1)
-    for _ in range(3):
+    for step in range(4):
         out = torch.zeros((B, Hq, 128), dtype=torch.bfloat16, device="cuda")
-        rc = _lib.load().cllo_gqa_exchange_combine_bf16(part.data_ptr(), gather, flags, 0, 1, 0, out.data_ptr(), rows, 128,
-                                                        None)
-        assert rc == 0
+        if step % 2 == 0:
+            rc = _lib.load().cllo_gqa_exchange_combine_bf16(part.data_ptr(), gather, flags, 0, 1, 0, out.data_ptr(),
+                                                            B, Hq, Hkv, 128, None)
+            assert rc == 0
+        else:
+            ops.gqa_decode_sharded(qd, kd, vd, gather, flags, 0, 1, epoch=0, scale=SCALE, kv_layout=1, out=out)
         torch.cuda.synchronize()
-        ol.assert_parity(to_bits(out), want, "exchange world=1")
+        ol.assert_parity(to_bits(out), want, "exchange world=1, step %d" % step)
     assert_clean_status()
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,workers", [(1, 6000, 64, 8, 0), (2, 1500, 40, 2, 37)])
+def test_two_rank_exchange_on_one_gpu_and_the_wait_that_runs_out(B, S, Hq, Hkv, workers):
+    """The two-rank protocol with both ranks' buffers on this GPU, one rank at a time (kernels that wait for one
+    another must not share a GPU).  Rank 1 goes first: it delivers its rows and then waits for a rank 0 that is
+    not there -- with the wait limit set to a few milliseconds the wait runs out, the kernel returns on its own,
+    the output rows are NaN and the device status names the exchange wait.  Then rank 0 runs the fused decode
+    (it finds rank 1's rows waiting), and rank 1 repeats its step (it now finds rank 0's): both must give the
+    unsharded result."""
+    import ctypes
+    import cuda_llm_ops_b200 as ops
+    from cuda_llm_ops_b200 import _lib
+    lib = _lib.load()
+    q = ol.randn_bf16((B, Hq, 128), 91)
+    k = ol.randn_bf16((B, S, Hkv, 128), 92, std=0.5)
+    v = ol.randn_bf16((B, S, Hkv, 128), 93, std=0.5)
+    want = ol.decode(q, k, v, SCALE, 0)
+    qd = to_dev(q)
+    cut = ops.shard_kv_positions(S, 2, 0)[1]
+    k0, v0 = to_dev(np.ascontiguousarray(k[:, :cut])), to_dev(np.ascontiguousarray(v[:, :cut]))
+    k1, v1 = to_dev(np.ascontiguousarray(k[:, cut:])), to_dev(np.ascontiguousarray(v[:, cut:]))
+    part1 = torch.zeros((B, Hq, 130), dtype=torch.float32, device="cuda")
+    ops.gqa_decode(qd, k1, v1, scale=SCALE, kv_layout=0, partial_out=part1)
+    buf_a, ga, fa = _exchange_buffers(2, B, Hq)  # rank 0's
+    buf_b, gb, fb = _exchange_buffers(2, B, Hq)  # rank 1's
+    arr = ctypes.c_void_p * 2
+    gather, flags = arr(ga, gb), arr(fa, fb)
+    out0 = torch.zeros((B, Hq, 128), dtype=torch.bfloat16, device="cuda")
+    out1 = torch.zeros((B, Hq, 128), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    assert_clean_status()
+    ops.set_exchange_wait_limit(4_000_000)  # about 2 ms
+    try:
+        rc = lib.cllo_gqa_exchange_combine_bf16(part1.data_ptr(), gather, flags, 1, 2, 1, out1.data_ptr(),
+                                                B, Hq, Hkv, 128, None)
+        assert rc == 0  # the launch itself succeeds; the time-out is a device-side status
+        rc, detail = ops.device_status()
+        assert rc == _lib.E_DEVICE_TIMEOUT and detail[2] == 8, (rc, detail)  # site 8: the exchange flag wait
+        assert torch.isnan(out1.float()).all()
+        assert ops.device_status()[0] == 0  # reading the status cleared it
+    finally:
+        ops.set_exchange_wait_limit(0)
+    ops.gqa_decode_sharded(qd, k0, v0, gather, flags, 0, 2, epoch=1, scale=SCALE, kv_layout=0, out=out0,
+                           num_workers=workers)
+    rc = lib.cllo_gqa_exchange_combine_bf16(part1.data_ptr(), gather, flags, 1, 2, 1, out1.data_ptr(),
+                                            B, Hq, Hkv, 128, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert_clean_status()
+    ol.assert_parity(to_bits(out0), want, "rank 0, fused")
+    ol.assert_parity(to_bits(out1), want, "rank 1, exchange from memory")
+    assert np.array_equal(to_bits(out0), to_bits(out1))  # same rows merged in the same order on both ranks
+    # an ordinary decode still works after the time-out
+    ol.assert_parity(_run(q, k, v, 0), want, "plain decode afterwards")

@@ -40,15 +40,18 @@ def _worker(rank, world, port, out_dir):
         dec = ops.KVShardedDecoder(exchange="nccl")
         out = dec.decode(qd, kd, vd, kv_layout=ops.KV_BSHD)
         torch.cuda.synchronize()
-        # the one-kernel exchange over peer memory must give the same answer, call after call (gather slots
-        # alternate by call parity, flag words carry a growing epoch)
-        peer = ops.KVShardedDecoder(exchange="auto")
-        peer_err = 0.0
-        for _ in range(5):
-            out_p = peer.decode(qd, kd, vd, kv_layout=ops.KV_BSHD)
-            torch.cuda.synchronize()
-            peer_err = max(peer_err, ol.errors(to_bits(out_p), to_bits(out))[0])
-        used_peer = 1.0 if peer.exchange == "peer" else 0.0
+        # the exchange over peer memory -- fused into the decode kernel, and from a stored partial -- must give
+        # the same answer, call after call (gather slots alternate by call parity, flag words carry a growing
+        # step number); the last calls check the device status as a caller would
+        peer_err, used_peer = 0.0, 1.0
+        for kind in ("auto", "peer"):
+            dec_p = ops.KVShardedDecoder(exchange=kind)
+            for i in range(5):
+                out_p = dec_p.decode(qd, kd, vd, kv_layout=ops.KV_BSHD, check=(i == 4))
+                torch.cuda.synchronize()
+                peer_err = max(peer_err, ol.errors(to_bits(out_p), to_bits(out))[0])
+            if dec_p.exchange != ("fused" if kind == "auto" else "peer"):
+                used_peer = 0.0
         single = ops.gqa_decode(to_dev(q), to_dev(k), to_dev(v), kv_layout=ops.KV_BSHD)
         torch.cuda.synchronize()
         want = ol.decode(q, k, v, SCALE, 0)
@@ -69,7 +72,7 @@ def test_two_gpu_position_sharded_decode_matches_oracle_and_single_gpu(tmp_path)
     for r in range(2):
         mx, mean, rel, mx1, mean1, rel1, rc, peer_err, used_peer = np.load(os.path.join(str(tmp_path), "r%d.npy" % r))
         assert rc == 0
-        assert peer_err <= 1e-6, peer_err  # same partials, same merge order: identical to the NCCL path
-        print("rank %d peer exchange in use: %s" % (r, bool(used_peer)))
+        assert peer_err <= 4e-3, peer_err  # same partials merged in another grouping: a bf16 ulp at most
+        assert used_peer == 1.0, "rank %d fell back to NCCL although the GPUs can map each other's memory" % r
         assert mx <= 2e-2 and mean <= 2e-3 and rel <= 2e-2, (r, mx, mean, rel)          # vs CPU oracle
         assert mx1 <= 4e-3 and rel1 <= 5e-3, (r, mx1, mean1, rel1)                       # vs the 1-GPU result
