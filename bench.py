@@ -4,7 +4,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Workloads (synthetic, seeded; shapes are the baseline configurations of this path):
-    decode_b60      GQA decode, B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D]   (default, headline)
+    all             (default) the headline decode_b60 line, and inside it -- under config.also_measured and
+                    roofline.others -- short runs of the other baseline configurations: prefill_nc (with its own
+                    end-to-end leg and CPU baseline), prefill_causal, decode_long, and on several GPUs decode_b60_strong
+                    (ONE batch of 60 split across the ranks) plus a parity check of the position-sharded decode
+                    against the single-GPU result and the CPU oracle
+    decode_b60      GQA decode, B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D]   (headline)
+    decode_b60_strong  the same shape as ONE batch of 60 sequences split 60/30/15/8,7 across the ranks (strong scaling)
     decode_long     one sequence, S=1,048,576, Hq=64, Hkv=8, KV sharded by position across GPUs
                     (all-gather of per-GPU partials + LSE combine; strong scaling)
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
@@ -37,10 +43,12 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on the headline
-# workload, from the ncu captures summarised under profiles/ (decode: 5 x the B=12 capture, traffic grows
-# with the K/V bytes; prefill: the capture of the workload itself).
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from one ncu capture each
+# (decode: 5 x a B=12 capture of the same kernel, traffic grows with the K/V bytes; prefill: a capture of the
+# workload itself).  A capture describes the kernel as it was when it was taken: "captured_at" says when.
 NCU_TRAFFIC_BYTES = {"decode_b60": 5 * 206_274_048, "prefill_nc": 19_081_728}
+NCU_TRAFFIC_CAPTURED_AT = {"decode_b60": "split-KV kernel with a separate merge launch (before the in-kernel merge)",
+                           "prefill_nc": "two-tile tcgen05 kernel, region-C version"}
 
 
 def measured_peaks():
@@ -121,7 +129,12 @@ def prefill_flops(B, Hq, Sq, Skv, D=128, causal=False):
     return f / 2 if causal else f
 
 
-def run_ours(args, rank, world, local_rank):
+def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
+    """Times one workload; returns its JSON line as a dict on rank 0 and None on the other ranks.
+
+    ``light`` (the extra workloads of the default run): no clock-sampling repeats, and an end-to-end leg and a CPU
+    baseline only where the line is asked to carry them (prefill_nc).
+    """
     import torch
     import torch.distributed as dist
     import cuda_llm_ops_b200 as ops
@@ -129,21 +142,44 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     peaks = measured_peaks()
-    wl = args.workload
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
 
-    def randn_bf16(shape, std=1.0):
+    def randn_bf16(shape, std=1.0, g=None):
         # generated in slices to keep the fp32 temporary small
+        g = g or gen
         out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
         flat = out.view(-1)
         step = 1 << 26
         for i in range(0, flat.numel(), step):
             n = min(step, flat.numel() - i)
-            flat[i:i + n] = (torch.randn(n, generator=gen, device=dev) * std).to(torch.bfloat16)
+            flat[i:i + n] = (torch.randn(n, generator=g, device=dev) * std).to(torch.bfloat16)
         return out
 
+    def seeded(seed):
+        return torch.Generator(device=dev).manual_seed(seed)
+
     extra = {}
-    if wl == "decode_b60":
+    if wl == "decode_b60_strong":
+        # baseline configuration 2 as stated: ONE batch of 60 sequences, split across the ranks (60 / 30 / 15 / 8,7)
+        S, Hq, Hkv = 4096, 128, 8
+        b0, b1 = ops.shard_batch(60, world, rank)
+        B = b1 - b0
+        layout = ops.KV_BSHD
+        q, k, v = randn_bf16((B, Hq, 128)), randn_bf16((B, S, Hkv, 128)), randn_bf16((B, S, Hkv, 128))
+        out = torch.empty_like(q)
+        step_fn = lambda: ops.gqa_decode(q, k, v, kv_layout=layout, out=out)  # noqa: E731
+        units_per_rank = decode_bytes(B, S, Hq, Hkv)
+        total_units = decode_bytes(60, S, Hq, Hkv)
+        metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
+        launches_per_step = 1
+        scaling = "strong"
+        config = {"workload": "decode_b60_strong: GQA decode, ONE batch of 60 sequences split across %d GPU(s) "
+                              "(this rank: %d), S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D], N(0,1) seeded" % (world, B),
+                  "global_batch": 60, "kv_seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "a rank's share at 8 GPUs (118-134 MB) is about the size of the 126 MB L2: the line says what "
+                        "a decode step of this batch costs, not an HBM figure"}
+        host_in = [q, k, v]
+    elif wl == "decode_b60":
         B, S, Hq, Hkv = (args.batch or 60), 4096, 128, 8
         layout = ops.KV_BSHD if args.layout == "bshd" else ops.KV_BHSD
         kshape = (B, S, Hkv, 128) if layout == ops.KV_BSHD else (B, Hkv, S, 128)
@@ -153,7 +189,7 @@ def run_ours(args, rank, world, local_rank):
         units_per_rank = decode_bytes(B, S, Hq, Hkv)
         total_units = units_per_rank * world
         metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
-        launches_per_step = 2
+        launches_per_step = 1  # the decode kernel (the merge runs inside it; a memset node zeroes its counters)
         scaling = "weak"
         config = {"workload": "decode_b60: GQA decode B=%d per GPU, S=4096, Hq=128, Hkv=8, D=128, one query token, "
                               "K/V %s, N(0,1) seeded" % (B, "[B,S,Hkv,D]" if layout == ops.KV_BSHD else "[B,Hkv,S,D]"),
@@ -163,27 +199,28 @@ def run_ours(args, rank, world, local_rank):
     elif wl == "decode_long":
         S_total, Hq, Hkv = (args.kv_len or (1 << 20)), 64, 8
         s0, s1 = ops.shard_kv_positions(S_total, world, rank)
-        q = randn_bf16((1, Hq, 128), 0.5)
-        if world > 1:
-            dist.broadcast(q, 0)
-        k, v = randn_bf16((1, s1 - s0, Hkv, 128), 0.5), randn_bf16((1, s1 - s0, Hkv, 128), 0.5)
+        # every tensor has its own seed (K and V per shard), so that rank 0 can rebuild the whole sequence for the
+        # single-GPU comparison below
+        q = randn_bf16((1, Hq, 128), 0.5, seeded(4000))
+        k = randn_bf16((1, s1 - s0, Hkv, 128), 0.5, seeded(5000 + 2 * rank))
+        v = randn_bf16((1, s1 - s0, Hkv, 128), 0.5, seeded(5001 + 2 * rank))
         dec = ops.KVShardedDecoder(exchange=args.exchange) if world > 1 else None
-        part = torch.zeros((1, 1, Hq, 130), dtype=torch.float32, device=dev)
         if world > 1:
             out = torch.empty_like(q)
             step_fn = lambda: dec.decode(q, k, v, kv_layout=ops.KV_BSHD, out=out)  # noqa: E731
-            launches_per_step = 3
+            launches_per_step = 1
         else:
             out = torch.empty_like(q)
             step_fn = lambda: ops.gqa_decode(q, k, v, kv_layout=ops.KV_BSHD, out=out)  # noqa: E731
-            launches_per_step = 2
+            launches_per_step = 1
         total_units = decode_bytes(1, S_total, Hq, Hkv)
         units_per_rank = decode_bytes(1, s1 - s0, Hq, Hkv)
         metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
         scaling = "strong"
         config = {"workload": "decode_long: one sequence, S=%d, Hq=64, Hkv=8, D=128, K/V [1,S,Hkv,D] 0.5*N(0,1)" % S_total,
                   "global_batch": 1, "kv_seq_len": S_total,
-                  "sharding": "KV positions; all-gather of (O,m,l) partials + LSE combine" if world > 1 else "none",
+                  "sharding": "KV positions; per-GPU (O,m,l) partials exchanged over peer memory (or NCCL all-gather) "
+                              "+ LSE combine" if world > 1 else "none",
                   "l2": "inputs exceed L2"}
         host_in = [q, k, v]
     elif wl == "swa":
@@ -344,11 +381,11 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step_fn()
     barrier()
-    if wl == "decode_long" and world > 1 and dec.exchange == "peer" and not args.no_graph:
-        # the three kernels of a step (decode, merge, exchange+combine) replayed from a CUDA graph: at ~100 us
+    if wl == "decode_long" and world > 1 and dec.exchange in ("peer", "fused") and not args.no_graph:
+        # a step (counters' memset + the fused decode/exchange kernel) replayed from a CUDA graph: at ~100 us
         # per step on 8 GPUs, host launch jitter between the ranks otherwise shows up as waiting in the exchange
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
@@ -374,9 +411,9 @@ def run_ours(args, rank, world, local_rank):
     t1 = torch.cuda.Event(enable_timing=True)
     if wl in ("prefill_nc", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"):
         # the L2 flush sits between iterations, so each step gets its own pair of events
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        for i in range(args.steps):
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
             flush.zero_()
             starts[i].record()
             inner()
@@ -386,12 +423,12 @@ def run_ours(args, rank, world, local_rank):
         total_ms = sum(per_step)
     else:
         t0.record()
-        for i in range(args.steps):
+        for i in range(steps):
             step_fn()
         t1.record()
         barrier()
         total_ms = t0.elapsed_time(t1)
-        per_step = [total_ms / args.steps]
+        per_step = [total_ms / steps]
     t_end = time.time()
     tt = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -399,8 +436,8 @@ def run_ours(args, rank, world, local_rank):
     total_ms = float(tt.item())
     # keep the GPUs busy with the same step a little longer so that the clock samples see load.  Every rank
     # runs the same number of repeats (the step may contain a collective), derived from the reduced time.
-    if total_ms < 600.0 and not args.profile:
-        reps = int(min(20000, 600.0 / max(total_ms / args.steps, 1e-3)))
+    if total_ms < 600.0 and not args.profile and not light:
+        reps = int(min(20000, 600.0 / max(total_ms / steps, 1e-3)))
         for _ in range(reps):
             step_fn()
         barrier()
@@ -408,12 +445,12 @@ def run_ours(args, rank, world, local_rank):
         extra["clock_sampling"] = "timed region + %d untimed repeats of the same step" % reps
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
-    ms_per_step = total_ms / args.steps
+    ms_per_step = total_ms / steps
     value = total_units / (ms_per_step * 1e-3) / scale_div
 
     # ---- end to end: pinned host buffers -> device -> kernel -> host ----
     e2e = None
-    if wl in ("decode_b60", "prefill_nc") and not args.profile:
+    if (wl == "prefill_nc" or (wl == "decode_b60" and not light)) and not args.profile:
         host = [t.cpu().pin_memory() for t in host_in]
         dev_in = [torch.empty_like(t) for t in host_in]
         out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
@@ -431,7 +468,7 @@ def run_ours(args, rank, world, local_rank):
                 ops.launch_flash_gqa_forward_bf16_kernel(dev_in[0], dev_in[1], dev_in[2], out=out, lse=lse, causal=False)
                 out_host.copy_(out, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
-        n_e2e = max(3, min(args.steps, 10))
+        n_e2e = max(3, min(steps, 10))
         e2e_step()
         barrier()
         e0 = torch.cuda.Event(enable_timing=True)
@@ -453,12 +490,17 @@ def run_ours(args, rank, world, local_rank):
     rc, detail = ops.device_status()
     if rc != 0:
         raise SystemExit("device status %d %s" % (rc, detail))
+    sharded_check = None
     if wl == "decode_long" and world > 1:
         config["exchange"] = dec.exchange
-        launches_per_step = 3 if dec.exchange == "peer" else 4  # decode, merge, exchange+combine | all-gather, combine
+        # kernels of this library per step -- fused: one | peer: decode + exchange | nccl: decode + combine
+        launches_per_step = 1 if dec.exchange == "fused" else 2
+        if not args.profile:
+            sharded_check = check_sharded_decode(ops, torch, dist, dev, rank, world, q, k, v, out, S_total, Hq, Hkv,
+                                                 randn_bf16, seeded, barrier)
 
     if rank != 0:
-        return
+        return None
     kernel_ms = statistics.mean(per_step)
     achieved = units_per_rank / (kernel_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
     peak = peaks["hbm_gbs"] if bound == "hbm" else peaks["bf16_tflops"]
@@ -466,7 +508,7 @@ def run_ours(args, rank, world, local_rank):
     roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                 "kernel": "rope_bf16_kernel" if wl == "rope" else "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
-                          "which also holds the merge pass and launch gaps" if bound == "hbm"
+                          "which also holds the counters' memset and launch gaps" if bound == "hbm"
                           else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
                                 else ("sgqa_fwd_kernel (bound by gathering 512 B per list entry out of L2, mma.sync "
                                       "products; the tensor peak is quoted for scale only)" if wl == "sgqa"
@@ -474,22 +516,79 @@ def run_ours(args, rank, world, local_rank):
                                             ("mla_fwd_kernel<128> (the one-tile kernel)" if wl == "prefill_chunk"
                                              else "prefill_fwd_kernel")))),
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(per_step)}
+    if traffic is not None:
+        roofline["traffic_captured_at"] = NCU_TRAFFIC_CAPTURED_AT.get(wl)
     if bound == "hbm":
         roofline["frac_of_nominal_8TBps"] = achieved / 8000.0
     else:
         roofline["frac_of_nominal_2250TF"] = achieved / 2250.0
         roofline["frac_of_sustained"] = achieved / peaks["bf16_tflops_sustained"]
 
-    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps,
+            "warmup": max(warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "roofline": roofline,
-            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "impl": "ours"}
+            "e2e": e2e, "gpu_launches": launches_per_step * steps, "clocks": clocks, "impl": "ours"}
     line["us_per_step"] = ms_per_step * 1e3
-    if wl == "decode_b60" and world == 1 and not args.no_cpu_baseline and not args.profile:
-        line["cpu_baseline"] = cpu_baseline_decode()
+    if e2e is not None:
+        # the end-to-end leg is bound by the host link: say what that link delivered on this rank
+        e2e["h2d_gbs_per_rank"] = e2e["h2d_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+    if sharded_check is not None:
+        line["sharded_check"] = sharded_check
+    if world == 1 and not args.no_cpu_baseline and not args.profile:
+        if wl == "decode_b60" and not light:
+            line["cpu_baseline"] = cpu_baseline_decode()
+        elif wl == "prefill_nc":
+            line["cpu_baseline"] = cpu_baseline_prefill_nc()
+        elif wl == "prefill_causal" and not light:
+            line["cpu_baseline"] = cpu_baseline_prefill_causal()
     if extra:
         line["extra"] = extra
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def check_sharded_decode(ops, torch, dist, dev, rank, world, q, k, v, out_sharded, S_total, Hq, Hkv, randn_bf16,
+                         seeded, barrier):
+    """The position-sharded result against the single-GPU result and the CPU oracle, and the single-GPU time of the
+    same sequence (the N=1 point of the strong-scaling curve, taken in the same run).  Rank 0 rebuilds the whole
+    sequence from the shards' seeds; the other ranks wait.  Returns a dict on rank 0, None elsewhere."""
+    import numpy as np
+    result = None
+    if rank == 0:
+        from gpu_util import to_bits
+        import oracle_lib as ol
+        kf = torch.empty((1, S_total, Hkv, 128), dtype=torch.bfloat16, device=dev)
+        vf = torch.empty_like(kf)
+        for r in range(world):
+            s0, s1 = ops.shard_kv_positions(S_total, world, r)
+            kf[:, s0:s1] = randn_bf16((1, s1 - s0, Hkv, 128), 0.5, seeded(5000 + 2 * r))
+            vf[:, s0:s1] = randn_bf16((1, s1 - s0, Hkv, 128), 0.5, seeded(5001 + 2 * r))
+        single = torch.empty_like(q)
+        for _ in range(3):
+            ops.gqa_decode(q, kf, vf, kv_layout=ops.KV_BSHD, out=single)
+        torch.cuda.synchronize()
+        n1 = 20
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n1):
+            ops.gqa_decode(q, kf, vf, kv_layout=ops.KV_BSHD, out=single)
+        t1.record()
+        torch.cuda.synchronize()
+        single_us = t0.elapsed_time(t1) / n1 * 1e3
+        mx, mean, rel = ol.errors(to_bits(out_sharded), to_bits(single))
+        # the CPU oracle on one kv head (its 8 query heads), the whole sequence
+        h = Hkv - 1
+        g = Hq // Hkv
+        qs = to_bits(q[:, h * g:(h + 1) * g])
+        ks, vs = to_bits(kf[:, :, h:h + 1]), to_bits(vf[:, :, h:h + 1])
+        want = ol.decode(qs, ks, vs, 1.0 / np.sqrt(128.0), 0)
+        omx, omean, orel = ol.errors(to_bits(out_sharded[:, h * g:(h + 1) * g]), want)
+        result = {"single_gpu_us_same_run": single_us,
+                  "vs_single_gpu": {"max_abs": mx, "mean_abs": mean, "rel_l2": rel},
+                  "vs_cpu_oracle_kv_head_%d" % h: {"max_abs": omx, "mean_abs": omean, "rel_l2": orel},
+                  "ok": bool(mx <= 4e-3 and rel <= 5e-3 and omx <= 2e-2 and omean <= 2e-3 and orel <= 2e-2)}
+        del kf, vf
+    barrier()
+    return result
 
 
 # ------------------------------------------------------------------------------------------------
@@ -542,6 +641,83 @@ def cpu_baseline_decode():
             "seconds": secs, "sample": "B=%d of the 60 sequences of the headline workload, C restatement" % B}
 
 
+def cpu_baseline_prefill_nc():
+    """The C restatement of upstream's torch forward reference (examples/python/Triton/test_flash_gqa_kernel.py:27-94,
+    mask made optional) on the whole non-causal baseline shape, all host threads."""
+    import numpy as np
+    import oracle_lib as ol
+    B, S, Hq, Hkv = 1, 4096, 16, 1
+    q, k, v = ol.randn_bf16((B, Hq, S, 128), 1), ol.randn_bf16((B, Hkv, S, 128), 2), ol.randn_bf16((B, Hkv, S, 128), 3)
+    t = time.perf_counter()
+    ol.prefill(q, k, v, 1.0 / np.sqrt(128.0), False)
+    secs = time.perf_counter() - t
+    return {"value": prefill_flops(B, Hq, S, S) / secs / 1e12, "unit": "TFLOP/s", "cores": ol.lib().cllo_oracle_num_threads(),
+            "kind": "port", "seconds": secs,
+            "sample": "the whole prefill_nc workload (B=1, S=4096, Hq=16, Hkv=1, non-causal), one run of the C "
+                      "restatement of upstream's forward reference"}
+
+
+def cpu_baseline_prefill_causal():
+    """The same restatement on a bounded sample of the causal baseline shape: the last 2048 query rows of one head."""
+    import numpy as np
+    import oracle_lib as ol
+    S, rows = 16384, 2048
+    q, k, v = ol.randn_bf16((1, 1, S, 128), 1), ol.randn_bf16((1, 1, S, 128), 2), ol.randn_bf16((1, 1, S, 128), 3)
+    t = time.perf_counter()
+    ol.prefill(q, k, v, 1.0 / np.sqrt(128.0), True, row_begin=S - rows, row_end=S)
+    secs = time.perf_counter() - t
+    flops = 4.0 * 128 * sum(range(S - rows + 1, S + 1))  # visible keys of those rows
+    return {"value": flops / secs / 1e12, "unit": "TFLOP/s", "cores": ol.lib().cllo_oracle_num_threads(), "kind": "port",
+            "seconds": secs, "sample": "query rows [%d, %d) of one (batch, head) of the causal shape (S=16384), C "
+                                       "restatement of upstream's forward reference" % (S - rows, S)}
+
+
+def run_ours(args, rank, world, local_rank):
+    """The default run: the headline line, carrying short runs of the other baseline configurations."""
+    import torch
+
+    def run(wl, steps, warmup, light):
+        res = measure(args, wl, rank, world, local_rank, steps, warmup, light)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        return res
+
+    if args.workload != "all":
+        line = run(args.workload, args.steps, args.warmup, False)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        return
+    line = run("decode_b60", args.steps, args.warmup, False)
+    plan = [("prefill_nc", 30), ("prefill_causal", 5), ("decode_long", 50)]
+    if world > 1:
+        plan.append(("decode_b60_strong", 100))
+    also, roof = {}, {}
+    for wl, steps in plan:
+        res = run(wl, steps, 5, True)
+        if rank != 0:
+            continue
+        r = res["roofline"]
+        entry = {"workload": res["config"]["workload"], "metric": res["metric"], "value": res["value"],
+                 "unit": res["unit"], "us_per_step": res["us_per_step"], "steps": res["steps"], "scaling": res["scaling"],
+                 "sharding": res["config"].get("sharding")}
+        for key in ("exchange", "launch"):
+            if key in res["config"]:
+                entry[key] = res["config"][key]
+        for key in ("e2e", "cpu_baseline", "sharded_check"):
+            if res.get(key) is not None:
+                entry[key] = res[key]
+        if wl == "decode_long" and res.get("sharded_check"):
+            entry["speedup_over_1_gpu_same_run"] = res["sharded_check"]["single_gpu_us_same_run"] / res["us_per_step"]
+        also[wl] = entry
+        roof[wl] = {"bound": r["bound"], "achieved_per_gpu": r["achieved"], "peak": r["peak"], "unit": r["unit"],
+                    "frac": r["frac"], "kernel_ms": r["kernel_ms"],
+                    "frac_of_nominal": r.get("frac_of_nominal_8TBps", r.get("frac_of_nominal_2250TF"))}
+    if rank == 0:
+        line["config"]["also_measured"] = also
+        line["roofline"]["others"] = roof
+        print(json.dumps(line), flush=True)
+
+
 def run_reference(args, rank, world):
     """Upstream's CPU implementation on the host cores; rank 0 only."""
     if rank != 0:
@@ -582,12 +758,12 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_b60",
-                    choices=["decode_b60", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
+    ap.add_argument("--workload", default="all",
+                    choices=["all", "decode_b60", "decode_b60_strong", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "peer", "nccl"],
                     help="decode_long on several GPUs: how the per-GPU partials are exchanged")
     ap.add_argument("--kv-len", type=int, default=0,
                     help="decode_long only: override the total KV length (profiling one GPU's share of a sharded run)")

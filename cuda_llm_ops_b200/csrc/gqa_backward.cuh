@@ -791,7 +791,12 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
                         ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + delta_bytes(B, Sq, Hq))
                         : nullptr;
     const long long blocks_kv = kv_tiles * p.head_splits;
-    if (blocks_dq > 0x7fffffffLL || blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+    // every grid size is checked before the first launch, so a refused call has written nothing
+    const long long tensor_elems = static_cast<long long>(B) * Hkv * Skv * kD;
+    const long long blocks_reduce = (2 * tensor_elems / 4 + 255) / 256;
+    if (blocks_dq > 0x7fffffffLL || blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL ||
+        (p.head_splits > 1 && blocks_reduce > 0x7fffffffLL))
+        return CLLO_E_UNSUPPORTED;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_do;
     if ((rc = prefill::encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
@@ -813,10 +818,7 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     if (p.head_splits > 1) {
-        const long long tensor_elems = static_cast<long long>(B) * Hkv * Skv * kD;
-        const long long blocks = (2 * tensor_elems / 4 + 255) / 256;
-        if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
-        bwd_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,
+        bwd_reduce_kernel<<<static_cast<unsigned>(blocks_reduce), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,
                                                                             p.dv, p.dk);
         CLLO_CUDA_TRY(cudaGetLastError());
     }

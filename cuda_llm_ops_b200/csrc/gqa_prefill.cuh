@@ -827,6 +827,9 @@ static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, in
 static int launch(const void* q, const void* k, const void* v, float scale, int causal, int window, const float* sink,
                   void* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
     if (window < 0) return CLLO_E_BAD_ARG;
+    // masked scores are +-infinity BEFORE the scale is folded into the exponent: a zero (or non-finite) scale would
+    // turn them into NaN, so it is refused
+    if (!(scale != 0.f) || !isfinite(scale)) return CLLO_E_BAD_ARG;
     if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
     if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return CLLO_E_BAD_ARG;
     if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;

@@ -516,6 +516,7 @@ static int launch_width(const void* q, const void* k, const void* v, float scale
 static int launch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse, int B,
                   int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, cudaStream_t stream) {
     if (!q || !k || !v || !o) return CLLO_E_BAD_ARG;
+    if (!(scale != 0.f) || !isfinite(scale)) return CLLO_E_BAD_ARG;  // masking relies on +-infinity times the scale
     if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Dqk <= 0 || Dv <= 0) return CLLO_E_BAD_ARG;
     if (Hq % Hkv != 0) return CLLO_E_BAD_ARG;
     if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16)) return CLLO_E_BAD_ARG;

@@ -177,6 +177,8 @@ int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer
  * (src/python/Triton/flash_gqa_kernel.py:16-138, :185-338).  Layout as upstream:
  *   q,o [B,Hq,Sq,D]   k,v [B,Hkv,Skv,D]   lse [B,Hq,Sq] fp32 (nullable)
  * causal != 0 keeps kv <= q (top-left aligned, flash_gqa_kernel.py:104,114).
+ * scale must be finite and non-zero (CLLO_E_BAD_ARG otherwise; negative is fine) -- here and in the sliding-window
+ * and MLA-shaped forwards below.
  */
 int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal,
                               void* o, float* lse,

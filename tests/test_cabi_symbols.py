@@ -43,6 +43,12 @@ def test_argument_validation_needs_no_gpu(built_library):
     assert lib.cllo_gqa_decode_bf16(None, None, None, 1.0, None, None, 0, 1, 1, 1, 1, 128, 0, 0, None, None) == _lib.E_BAD_ARG
     assert lib.cllo_gqa_combine_bf16(None, 1, None, 1, 128, None) == _lib.E_BAD_ARG
     assert lib.cllo_gqa_prefill_fwd_bf16(None, None, None, 1.0, 0, None, None, 1, 1, 1, 1, 1, 128, None) == _lib.E_BAD_ARG
+    # a zero or non-finite softmax scale is refused by the forward launchers (masking multiplies infinities by it)
+    for bad in (0.0, float("inf"), float("nan")):
+        assert lib.cllo_gqa_prefill_fwd_bf16(1 << 20, 1 << 20, 1 << 20, bad, 1, 1 << 20, None, 1, 256, 256, 4, 4, 128,
+                                             None) == _lib.E_BAD_ARG
+        assert lib.cllo_mla_prefill_fwd_bf16(1 << 20, 1 << 20, 1 << 20, bad, 1, 1 << 20, None, 1, 256, 256, 4, 4, 192,
+                                             128, None) == _lib.E_BAD_ARG
     assert lib.cllo_status_string(_lib.E_WORKSPACE).decode().startswith("workspace")
     # peer exchange: null tables, rank outside the world, epoch 0, too many peers
     two = (ctypes.c_void_p * 2)(1 << 20, 2 << 20)
