@@ -15,6 +15,7 @@ E_CUDA = -4
 E_DEVICE_TIMEOUT = -6
 KV_BSHD = 0
 KV_BHSD = 1
+WS_COUNTERS_ZERO = 0x100
 
 _lib = None
 

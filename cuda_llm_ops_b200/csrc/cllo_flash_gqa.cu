@@ -18,7 +18,7 @@ using namespace cllo;
 // the library carries these ~2.5 MiB until the process exits.  Host code must never hand this NAME to
 // a kernel: on the host it is only a stand-in, the device address comes from cudaGetSymbolAddress.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[
-    static_cast<size_t>(CLLO_NOALLOC_MAX_WORKERS) * (2 * decode::kSlotFloats * sizeof(float) + sizeof(unsigned))];
+    decode::kSlotOffsetBytes + static_cast<size_t>(CLLO_NOALLOC_MAX_WORKERS) * 2 * decode::kSlotFloats * sizeof(float)];
 static void* g_noalloc_ptr[kMaxDevices];  // device address of the array, looked up once per device
 static std::mutex g_noalloc_mutex;
 
@@ -121,6 +121,8 @@ static int decode_launch(const void* q, const void* k, const void* v, float scal
                          size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout, int num_workers,
                          float* partial_out, const shard::Params* sp, cudaStream_t st) {
     if (!q || !k || !v || (!o && !partial_out)) return CLLO_E_BAD_ARG;
+    const bool counters_zero = (kv_layout & CLLO_WS_COUNTERS_ZERO) != 0;
+    kv_layout &= ~CLLO_WS_COUNTERS_ZERO;
     if (kv_layout != CLLO_KV_BSHD && kv_layout != CLLO_KV_BHSD) return CLLO_E_BAD_ARG;
     if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || (o && !aligned_to(o, 16)) ||
         (partial_out && !aligned_to(partial_out, 8)))
@@ -138,7 +140,8 @@ static int decode_launch(const void* q, const void* k, const void* v, float scal
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.o = static_cast<__nv_bfloat16*>(o);
     p.partial_out = partial_out;
-    p.ws = static_cast<float*>(workspace);
+    p.ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.slot_offset);
+    p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + plan.counter_offset);
     p.scale_log2 = scale * decode::kLog2e;
     p.kv_layout = kv_layout;
 
@@ -164,8 +167,9 @@ static int decode_launch(const void* q, const void* k, const void* v, float scal
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
         di->decode_attr_set = true;
     }
-    // arrival counters of the units that a worker boundary cuts
-    if (plan.needs_merge)
+    // arrival counters of the units that a worker boundary cuts: zero at kernel start.  The kernel leaves them
+    // zero, so a caller that keeps a workspace for this library alone can vouch for them and save the memset node.
+    if (plan.needs_merge && !(counters_zero && plan.counters_fixed))
         CLLO_CUDA_TRY(cudaMemsetAsync(static_cast<char*>(workspace) + plan.counter_offset, 0, plan.counter_bytes, st));
     if (sp) {
         decode::decode_splitkv_kernel<true><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p, *sp);
@@ -304,8 +308,12 @@ int cllo_gqa_decode_bf16_noalloc(const void* q, const void* k, const void* v, fl
         }
         scratch = g_noalloc_ptr[dev];
     }
-    if (num_workers <= 0)
-        num_workers = di->sm_count < CLLO_NOALLOC_MAX_WORKERS ? di->sm_count : CLLO_NOALLOC_MAX_WORKERS;
+    if (num_workers <= 0) {
+        decode::Plan plan;
+        rc = decode::make_plan(B, S, Hq, Hkv, D, 0, di->sm_count, &plan);
+        if (rc != CLLO_OK) return rc;
+        num_workers = plan.prm.W < CLLO_NOALLOC_MAX_WORKERS ? plan.prm.W : CLLO_NOALLOC_MAX_WORKERS;
+    }
     return cllo_gqa_decode_bf16(q, k, v, scale, o, scratch, sizeof(g_noalloc_scratch), B, S, Hq, Hkv, D, kv_layout,
                                 num_workers, nullptr, stream);
 }

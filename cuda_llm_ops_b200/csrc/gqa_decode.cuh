@@ -41,7 +41,10 @@ namespace decode {
 
 constexpr int kD = 128;
 constexpr int kTok = 64;                     // tokens per stage
-constexpr int kStages = 6;
+#ifndef CLLO_DECODE_STAGES
+#define CLLO_DECODE_STAGES 6
+#endif
+constexpr int kStages = CLLO_DECODE_STAGES;
 constexpr int kGroups = 2;                   // consumer groups; kStages must be a multiple of it so that a
                                              // stage buffer is always drained by the same group, in order
 constexpr int kWarpsPerGroup = 4;
@@ -68,7 +71,8 @@ struct Params {
     const __nv_bfloat16* q;
     __nv_bfloat16* o;
     float* partial_out;  // nullable
-    float* ws;           // [W][2][16][D+2] partial slots, then [W] uint32 arrival counters (zero at kernel start)
+    float* ws;           // [W][2][16][D+2] partial slots
+    unsigned* counters;  // [W] arrival counters, zero at kernel start and again at its end
     float scale_log2;    // scale * log2(e)
     int B, S, Hq, Hkv, G, n_gblk, n_t, kv_layout, W;
     long long T;  // total tiles
@@ -94,7 +98,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     float* xchg = reinterpret_cast<float*>(gen_base + kSmemXchg);
     const uint32_t bar_base = base + kSmemBar;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + 2 * kStages * 8);
-    volatile int* misc = abort_flag + 1;  // [0] this block merges the unit, [1] step number (sharded mode)
+    volatile int* misc = abort_flag + 1;  // [0] this block merges the unit, [1] step number (sharded mode, set once)
     auto full_bar = [&](int s) { return bar_base + s * 8; };
     auto empty_bar = [&](int s) { return bar_base + (kStages + s) * 8; };
 
@@ -108,6 +112,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             mbar_init(empty_bar(s), kWarpsPerGroup);
         }
         *abort_flag = 0;
+        if (kSharded) misc[1] = static_cast<int>(shard::read_epoch(sp));
         fence_mbar_init();
     }
     __syncthreads();
@@ -398,25 +403,34 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         // ---- this worker's piece of the unit is in the workspace: count it in; the last one to arrive merges ----
         const long long w_first = worker_of_tile(unit_lo, p.T, p.W), w_last = worker_of_tile(unit_hi - 1, p.T, p.W);
         const int n_pieces = static_cast<int>(w_last - w_first) + 1;
-        __threadfence();
+        unsigned* counter = p.counters + w_first;
+        // the barrier orders every thread's stores before thread 0's fence, which is cumulative: whoever sees the
+        // count sees the piece
         named_bar_sync(1, kConsumerWarps * 32);
         if (threadIdx.x == 0) {
-            unsigned* counters = reinterpret_cast<unsigned*>(p.ws + static_cast<size_t>(p.W) * 2 * kSlotFloats);
-            const bool last = n_pieces == 1 || atomicAdd(counters + w_first, 1u) == static_cast<unsigned>(n_pieces - 1);
+            bool last = n_pieces == 1;
+            if (!last) {
+                __threadfence();
+                last = atomicAdd(counter, 1u) == static_cast<unsigned>(n_pieces - 1);
+                __threadfence();
+                if (last) *counter = 0u;  // the counters are zero again when the kernel ends
+            }
             misc[0] = last ? 1 : 0;
-            if (kSharded && last) misc[1] = static_cast<int>(shard::take_epoch(sp));  // one ticket per unit
         }
         named_bar_sync(1, kConsumerWarps * 32);
         if (misc[0] == 0) continue;
-        __threadfence();
         {
             const int tid = threadIdx.x, mrow_i = tid >> 4, c8 = (tid & 15) * 8;
             const int which_first = (worker_lo(w_first, p.T, p.W) == unit_lo) ? 0 : 1;
             float mg[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, mm = -INFINITY, ll = 0.f;
             if (mrow_i < rows) {
-                shard::merge_rows(n_pieces, c8, [&](int i) {
+                auto piece = [&](int i) {
                     return p.ws + ((w_first + i) * 2 + (i == 0 ? which_first : 0)) * kSlotFloats + mrow_i * kPW;
-                }, mg, mm, ll);
+                };
+                if (n_pieces <= 4)
+                    shard::merge_rows<4>(n_pieces, c8, piece, mg, mm, ll);
+                else
+                    shard::merge_rows<8>(n_pieces, c8, piece, mg, mm, ll);
             }
             if (kSharded) {
                 shard::publish_wait_combine(sp, static_cast<unsigned>(misc[1]), 1, tid, u, head0, rows, mg, mm, ll, p.o);
@@ -454,14 +468,41 @@ __global__ void __launch_bounds__(kD) combine_rows_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
+// Workspace layout: kFixedCounters arrival counters at the very start -- a fixed place, so that a workspace that
+// serves calls with different worker counts keeps its counters apart from its partial slots -- then the slots; a
+// call with more workers than that keeps its counters behind the slots instead.
+constexpr int kFixedCounters = 1024;
+constexpr size_t kSlotOffsetBytes = kFixedCounters * sizeof(unsigned);
+
 struct Plan {
     Params prm;
-    size_t ws_bytes;        // partial slots + arrival counters
-    size_t counter_offset;  // byte offset of the counters inside the workspace
+    size_t ws_bytes;        // arrival counters + partial slots
+    size_t slot_offset;     // byte offset of the partial slots inside the workspace
+    size_t counter_offset;  // byte offset of the counters
     size_t counter_bytes;
+    bool counters_fixed;    // the counters sit in the fixed area at the start
     bool needs_merge;       // some unit is cut by a worker boundary
     long long units;
 };
+
+// How many persistent blocks to launch when the caller leaves the choice to the library.  Measured on B200
+// (148 SMs, six 32 KB stages per block): the memory system is saturated from about 0.7 x SMs blocks on, and more
+// than about 0.87 x SMs blocks (768 stages in flight) cost 3-7 % again; within that window a count that cuts no
+// unit (whole units per worker: no partials, no merge) or, failing that, cuts every unit in the same places (the
+// workers of different kv heads then walk the same token positions together, and with K/V [B,S,Hkv,D] those are
+// the same DRAM rows) is another ~5 % faster than an arbitrary one.
+static long long choose_workers(long long T, long long units, int sm_count) {
+    long long hi = (static_cast<long long>(sm_count) * 173) / 200;
+    if (hi < 1) hi = 1;
+    if (T <= hi) return T;
+    long long lo = (static_cast<long long>(sm_count) * 7) / 10;
+    if (lo < 1) lo = 1;
+    for (long long W = hi; W >= lo; --W)
+        if (units % W == 0) return W;
+    for (long long W = hi; W >= lo; --W)
+        if (W % units == 0) return W;
+    return hi;
+}
 
 static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int sm_count, Plan* plan) {
     if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || num_workers < 0) return CLLO_E_BAD_ARG;
@@ -478,14 +519,17 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     plan->units = static_cast<long long>(B) * Hkv * p.n_gblk;
     if (plan->units * kRows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
     p.T = plan->units * p.n_t;
-    long long W = num_workers > 0 ? num_workers : sm_count;
+    long long W = num_workers > 0 ? num_workers : choose_workers(p.T, plan->units, sm_count);
     if (W > p.T) W = p.T;
     if (W < 1) W = 1;
     p.W = static_cast<int>(W);
     if (p.T / W + 1 > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;  // a worker's tile count is a 32-bit loop index
-    plan->counter_offset = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
+    const size_t slot_bytes = static_cast<size_t>(W) * 2 * kSlotFloats * sizeof(float);
+    plan->slot_offset = kSlotOffsetBytes;
     plan->counter_bytes = static_cast<size_t>(W) * sizeof(unsigned);
-    plan->ws_bytes = plan->counter_offset + plan->counter_bytes;
+    plan->counters_fixed = W <= kFixedCounters;
+    plan->counter_offset = plan->counters_fixed ? 0 : kSlotOffsetBytes + slot_bytes;
+    plan->ws_bytes = kSlotOffsetBytes + slot_bytes + (plan->counters_fixed ? 0 : plan->counter_bytes);
     plan->needs_merge = false;
     for (long long w = 1; w < W; ++w)
         if (worker_lo(w, p.T, W) % p.n_t != 0) {

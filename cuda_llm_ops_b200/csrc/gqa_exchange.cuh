@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(shard::kThreads) exchange_combine_kernel(const
     const long long head0 = static_cast<long long>(b) * geo.Hq + static_cast<long long>(kvh) * geo.G +
                             gblk * shard::kRowsPerUnit;
     __shared__ unsigned s_epoch;
-    if (threadIdx.x == 0) s_epoch = shard::take_epoch(sp);
+    if (threadIdx.x == 0) s_epoch = shard::read_epoch(sp);
     __syncthreads();
     const int tid = threadIdx.x, row = tid >> 4, c8 = (tid & 15) * 8;
     float val[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, m = -INFINITY, l = 0.f;

@@ -5,7 +5,7 @@
 // Every rank owns, in memory that all ranks of the node can address,
 //   gather  [2 parities][world][rows][D+2] fp32   slot [e & 1][r] = rank r's packed (O, m, l) rows of step e
 //   flags   [world][CLLO_SHARD_MAX_UNITS] uint32   flag [r][u] = last step whose rows of unit u rank r has delivered
-//           followed by one launch-ticket word
+//           followed by one word that counts the units this rank has completed since the buffers were zeroed
 // A "unit" is one (batch, kv head, block of <= 16 query heads): the rows that one thread block finishes together.
 // The block that holds unit u's merged rows stores them into slot [e & 1][rank] of EVERY rank's gather buffer with
 // plain peer stores, fences at system scope, raises flag [rank][u] = e on every rank, then waits (bounded) until the
@@ -61,19 +61,19 @@ __device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
 }
 
 // Log-sum-exp merge of n packed rows for one thread's 8 columns.  row_ptr(i) is the i-th row (D+2 floats, 8-byte
-// aligned, read through L2 because other blocks or other GPUs wrote it).  Rows are taken four at a time so that
+// aligned, read through L2 because other blocks or other GPUs wrote it).  Rows are taken kGroup at a time so that
 // their loads are in flight together; the running reference is raised between groups, always in the same order, so
 // the result does not depend on which block does the merge.  m is in natural-log units, rows with l == 0 are skipped.
-template <typename RowPtr>
+template <int kGroup, typename RowPtr>
 __device__ __forceinline__ void merge_rows(int n, int c8, RowPtr row_ptr, float (&acc)[8], float& m_out, float& l_out) {
     float mrun = -INFINITY, lrun = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 #pragma unroll 1
-    for (int i0 = 0; i0 < n; i0 += 4) {
-        float2 ml[4], d[4][4];
+    for (int i0 = 0; i0 < n; i0 += kGroup) {
+        float2 ml[kGroup], d[kGroup][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kGroup; ++i) {
             const int ii = (i0 + i < n) ? i0 + i : n - 1;
             const float* row = row_ptr(ii);
             ml[i] = __ldcg(reinterpret_cast<const float2*>(row + kD));
@@ -83,13 +83,13 @@ __device__ __forceinline__ void merge_rows(int n, int c8, RowPtr row_ptr, float 
         }
         float mnew = mrun;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mnew = fmaxf(mnew, ml[i].y > 0.f ? ml[i].x : -INFINITY);
+        for (int i = 0; i < kGroup; ++i) mnew = fmaxf(mnew, ml[i].y > 0.f ? ml[i].x : -INFINITY);
         const float keep = (mrun == -INFINITY) ? 0.f : __expf(mrun - mnew);
         lrun *= keep;
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] *= keep;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kGroup; ++i) {
             const float wgt = ml[i].y > 0.f ? __expf(ml[i].x - mnew) : 0.f;
             lrun += wgt * ml[i].y;
 #pragma unroll
@@ -120,14 +120,19 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* dst, int c8, const
     *reinterpret_cast<uint4*>(dst + c8) = pk;
 }
 
-// The step number of this launch.  Every launch raises the ticket word `units` times (once per unit), so the
-// blocks of the n-th launch all derive n; a call sequence that never changes its arguments (a CUDA graph) can
-// therefore pass epoch = 0.  Call with one thread per unit.
-__device__ __forceinline__ unsigned take_epoch(const Params& sp) {
-    if (sp.epoch) return sp.epoch;
-    unsigned* ticket = sp.flags[sp.rank] + static_cast<size_t>(sp.world) * kMaxUnits;
-    return atomicAdd(ticket, 1u) / static_cast<unsigned>(sp.units) + 1u;
+// The step number of a launch.  With epoch == 0 it comes from the completion counter: every launch completes
+// `units` units and raises the counter once for each (count_unit_done, after the unit's output is written), and
+// launches on a stream do not overlap, so at the start of the n-th launch the counter reads (n-1) * units.  A call
+// sequence that never changes its arguments (a CUDA graph) can therefore pass epoch = 0.  Read it once per block,
+// at kernel start, where its latency hides under the set-up.
+__device__ __forceinline__ unsigned* done_counter(const Params& sp) {
+    return sp.flags[sp.rank] + static_cast<size_t>(sp.world) * kMaxUnits;
 }
+__device__ __forceinline__ unsigned read_epoch(const Params& sp) {
+    if (sp.epoch) return sp.epoch;
+    return *reinterpret_cast<volatile unsigned*>(done_counter(sp)) / static_cast<unsigned>(sp.units) + 1u;
+}
+__device__ __forceinline__ void count_unit_done(const Params& sp) { atomicAdd(done_counter(sp), 1u); }
 
 // Publish this rank's rows of unit u (thread tid holds columns [c8, c8+8) of row head0 + tid / 16), wait for the
 // other ranks' rows of the same unit and write the merged bf16 output.  All kThreads threads of the block call it
@@ -143,7 +148,8 @@ __device__ __forceinline__ void publish_wait_combine(const Params& sp, unsigned 
         const size_t off = par + static_cast<size_t>(sp.rank) * slot_floats + static_cast<size_t>(head0 + row) * kPW;
         for (int p = 0; p < sp.world; ++p) store_packed_row(sp.gather[p] + off, c8, val, m, l);
     }
-    __threadfence_system();
+    // the barrier orders every thread's row stores before the flag stores below, and a release at system scope is
+    // cumulative over that order: a peer that acquires the flag sees the rows
     named_bar_sync(bar_id, kThreads);
     bool late = false;
     if (tid < sp.world) {
@@ -160,6 +166,7 @@ __device__ __forceinline__ void publish_wait_combine(const Params& sp, unsigned 
         }
     }
     late = named_bar_or(bar_id, kThreads, late);
+    if (tid == 0) count_unit_done(sp);
     if (row >= rows) return;
     __nv_bfloat16* dst = o + static_cast<size_t>(head0 + row) * kD;
     if (late) {
@@ -169,7 +176,7 @@ __device__ __forceinline__ void publish_wait_combine(const Params& sp, unsigned 
     }
     const float* mine = sp.gather[sp.rank] + par + static_cast<size_t>(head0 + row) * kPW;
     float acc[8], mm, ll;
-    merge_rows(sp.world, c8, [&](int s) { return mine + static_cast<size_t>(s) * slot_floats; }, acc, mm, ll);
+    merge_rows<8>(sp.world, c8, [&](int s) { return mine + static_cast<size_t>(s) * slot_floats; }, acc, mm, ll);
     store_bf16_row(dst, c8, acc, ll);
 }
 

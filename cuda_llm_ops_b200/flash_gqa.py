@@ -15,6 +15,7 @@ torch is used for device memory and streams only.  Nothing here computes attenti
 is no fallback: without the compiled library or on a non-CUDA tensor these functions raise.
 """
 import math
+import threading
 
 import torch
 
@@ -26,6 +27,7 @@ HEAD_DIM = 128
 PARTIAL_WIDTH = HEAD_DIM + 2
 
 _workspaces = {}
+_workspaces_lock = threading.Lock()
 
 
 def _stream_ptr():
@@ -43,10 +45,13 @@ def _workspace(device, nbytes):
     streams that may overlap on the GPU must each pass their own.
     """
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    with _workspaces_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            # zeroed once: the decode kernel leaves its arrival counters zero, so calls on this tensor may vouch
+            # for them (WS_COUNTERS_ZERO) and skip the memset in front of every kernel
+            ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
     return ws
 
 
@@ -92,6 +97,7 @@ def gqa_decode(q, k, v, scale=None, kv_layout=KV_BHSD, out=None, partial_out=Non
         nbytes = decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers)
         if workspace is None:
             workspace = _workspace(q.device, nbytes)
+            kv_layout |= _lib.WS_COUNTERS_ZERO
         if partial_out is not None:
             if partial_out.dtype != torch.float32 or tuple(partial_out.shape) != (B, Hq, D + 2) \
                     or not partial_out.is_contiguous() or not partial_out.is_cuda:
@@ -129,6 +135,7 @@ def gqa_decode_sharded(q, k_local, v_local, peer_gather, peer_flags, rank, world
         nbytes = decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers)
         if workspace is None:
             workspace = _workspace(q.device, nbytes)
+            kv_layout |= _lib.WS_COUNTERS_ZERO
         rc = _lib.load().cllo_gqa_decode_sharded_bf16(
             q.data_ptr(), k_local.data_ptr(), v_local.data_ptr(), float(scale), out.data_ptr(),
             workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, S, Hq, Hkv, D, kv_layout,
@@ -604,4 +611,9 @@ def device_status():
     import ctypes
     detail = (ctypes.c_int * 4)()
     rc = _lib.load().cllo_device_status(detail)
+    if rc != 0:
+        # a kernel gave up half-way: the cached workspaces may hold counts of pieces that never got merged
+        with _workspaces_lock:
+            for ws in _workspaces.values():
+                ws.zero_()
     return rc, list(detail)

@@ -32,6 +32,13 @@ extern "C" {
 #define CLLO_KV_BSHD 0 /* [B, S, Hkv, D]  upstream C++ layout (decode_flash_gqa_kernel.cu:144-148) */
 #define CLLO_KV_BHSD 1 /* [B, Hkv, S, D]  upstream Triton layout (decode_flash_gqa_kernel.py:50-53) */
 
+/* May be OR-ed into a decode call's kv_layout: the caller vouches that the arrival counters (the first 4 KB of
+ * the workspace) are zero -- it zeroed the workspace once (cudaMemset of all of it is fine) and since then nothing but
+ * calls of this library, none of which ended in CLLO_E_DEVICE_TIMEOUT, has written to it.  The call then skips the
+ * memset node it would otherwise put in front of the kernel (the kernel leaves the counters zero).  Ignored when
+ * num_workers exceeds 1024. */
+#define CLLO_WS_COUNTERS_ZERO 0x100
+
 /* Width of one packed partial row: D un-normalised fp32 outputs, then m, then l. */
 #define CLLO_PARTIAL_WIDTH(D) ((D) + 2)
 
@@ -62,8 +69,10 @@ int cllo_shutdown(void);
  *       shares for `num_workers` persistent thread blocks; shares that cover only part of a head leave
  *       fp32 partials (O, m, l) in the workspace, and the last block to finish a head's share merges them
  *       by log-sum-exp (second pass, same kernel; the call zeroes its arrival counters with a memset node
- *       on `stream` first).  Calls that may overlap on the GPU need a workspace each.
- *   num_workers: 0 = one per SM of the current device.
+ *       on `stream` first, unless kv_layout carries CLLO_WS_COUNTERS_ZERO).  Calls that may overlap on the
+ *       GPU need a workspace each.
+ *   num_workers: 0 = chosen by the library: between 0.7 and 0.87 blocks per SM of the current device,
+ *       preferring a count that gives every block whole (batch, kv head) units or equal cuts of them.
  *   Group sizes above 16: the query heads of a group are served in blocks of 16 and each block streams the
  *       group's K/V again, so G = 32 reads K/V twice (no upstream configuration has G > 16).
  *   partial_out (nullable): when given, `o` is ignored and the call writes, for every (b, h), one
@@ -97,16 +106,16 @@ int cllo_gqa_decode_bf16_compat(const void* q, const void* k, const void* v, flo
  * of device memory to its KV-cache pool and forbids plugins to allocate; a latency-critical decode loop
  * that cannot afford the device-wide synchronisation a cudaMalloc/cudaFree implies; a caller that only
  * receives the tensors' pointers.  For them this variant keeps the split-KV partials in a fixed
- * __device__ array inside the library (CLLO_NOALLOC_MAX_WORKERS * 16,640 bytes, about 2.5 MiB, resident
+ * __device__ array inside the library (4 KB + CLLO_NOALLOC_MAX_WORKERS * 16,640 bytes, about 2.5 MiB, resident
  * on every GPU that loads the library until the process exits).  It calls neither cudaMalloc nor
  * cudaFree nor any allocating routine.
  *
  * Same arguments and results as cllo_gqa_decode_bf16 without workspace and partial_out.  Limits:
  *   - num_workers > CLLO_NOALLOC_MAX_WORKERS is refused with CLLO_E_WORKSPACE (the partials would not
- *     fit); num_workers == 0 uses min(SM count, CLLO_NOALLOC_MAX_WORKERS).  B, S and the head counts are
- *     not limited by the scratch: its size depends on the number of workers only.  On a GPU with more
- *     than CLLO_NOALLOC_MAX_WORKERS SMs the default therefore leaves SMs idle and the call is slower than
- *     cllo_gqa_decode_bf16 with a workspace.
+ *     fit); num_workers == 0 uses min(the library's own choice, CLLO_NOALLOC_MAX_WORKERS).  B, S and the head counts are
+ *     not limited by the scratch: its size depends on the number of workers only.  On a GPU with so many
+ *     SMs that the library would choose more than CLLO_NOALLOC_MAX_WORKERS blocks (about 185 SMs and up) the
+ *     default is capped and the call is slower than cllo_gqa_decode_bf16 with a workspace.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *     device current) and remembers it; make that first call outside any stream capture.
  *   - All calls on one device share the one array and it keeps the previous call's contents.  The only
@@ -136,12 +145,12 @@ int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long 
  * Buffers, per rank, in memory that every rank has mapped (CUDA IPC, symmetric memory, ...), zeroed once before
  * the first step:
  *   gather  cllo_gqa_shard_gather_bytes(world, B, Hq, D) bytes: [2][world][B*Hq][D+2] fp32
- *   flags   cllo_gqa_shard_flag_bytes(world) bytes: [world][CLLO_SHARD_MAX_UNITS] uint32 + one ticket word
+ *   flags   cllo_gqa_shard_flag_bytes(world) bytes: [world][CLLO_SHARD_MAX_UNITS] uint32 + one counter word
  * peer_gather / peer_flags are HOST arrays of `world` device pointers, entry p = rank p's buffer as mapped into
  * THIS process; entry `rank` is the local one.  B * Hkv * ceil((Hq/Hkv)/16) must not exceed CLLO_SHARD_MAX_UNITS.
  *
  *   epoch: 1, 2, 3, ... the same on every rank for the same step; or 0 on every rank and every step, in which case
- *       the kernels count their own launches in the ticket word (a call sequence that never changes its arguments,
+ *       the kernels derive the step from a completion counter in the flag buffer (a call sequence that never changes its arguments,
  *       e.g. one replayed from a CUDA graph).  Every rank must make one call per step.  A rank that is late by more
  *       than the wait limit (about a second unless changed by cllo_set_exchange_wait_limit) makes the others' wait
  *       expire: their output rows are filled with NaN and cllo_device_status() reports CLLO_E_DEVICE_TIMEOUT.

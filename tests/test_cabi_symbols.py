@@ -76,17 +76,23 @@ def test_decode_plan_balances_tiles(built_library):
     # the headline decode shape on a 148-SM part
     assert lib.cllo_gqa_decode_plan(60, 4096, 128, 8, 128, 0, 148, plan) == 0
     W, n_t, T, merge, tok = plan[0], plan[1], plan[2] | (plan[3] << 32), plan[4], plan[5]
-    assert (W, tok, n_t, T, merge) == (148, 64, 64, 60 * 8 * 64, 1)
+    # 480 (batch, kv head) units: the library picks 120 blocks of four whole units each, nothing to merge
+    assert (W, tok, n_t, T, merge) == (120, 64, 64, 60 * 8 * 64, 0)
+    # an explicit count is taken as given; shares differ by at most one tile
+    assert lib.cllo_gqa_decode_plan(60, 4096, 128, 8, 128, 148, 148, plan) == 0 and plan[0] == 148 and plan[4] == 1
+    W = 148
     shares = [((w + 1) * T) // W - (w * T) // W for w in range(W)]
     assert max(shares) - min(shares) <= 1 and sum(shares) == T
+    # one long sequence, 8 kv heads: 128 blocks, every head cut into 16 equal pieces
+    assert lib.cllo_gqa_decode_plan(1, 1 << 20, 64, 8, 128, 0, 148, plan) == 0 and plan[0] == 128 and plan[4] == 1
     # fewer tiles than workers: the worker count shrinks to the tile count
     assert lib.cllo_gqa_decode_plan(1, 100, 4, 1, 128, 0, 148, plan) == 0 and plan[0] == 2
     # whole units per worker: no merge pass
     assert lib.cllo_gqa_decode_plan(4, 1024, 32, 8, 128, 32, 148, plan) == 0 and plan[4] == 0
     assert lib.cllo_gqa_decode_plan(1, 64, 6, 4, 128, 0, 148, plan) == _lib.E_BAD_ARG
     assert lib.cllo_gqa_decode_plan(1, 64, 4, 4, 64, 0, 148, plan) == _lib.E_UNSUPPORTED
-    # partial slots plus one arrival counter per worker
-    assert lib.cllo_gqa_decode_workspace_bytes(60, 4096, 128, 8, 128, 148) == 148 * (2 * 16 * 130 * 4 + 4)
+    # 4 KB of arrival counters, then two partial slots per worker
+    assert lib.cllo_gqa_decode_workspace_bytes(60, 4096, 128, 8, 128, 148) == 4096 + 148 * 2 * 16 * 130 * 4
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
