@@ -44,10 +44,10 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from one ncu capture each
-# (decode: 5 x a B=12 capture of the same kernel, traffic grows with the K/V bytes; prefill: a capture of the
-# workload itself).  A capture describes the kernel as it was when it was taken: "captured_at" says when.
-NCU_TRAFFIC_BYTES = {"decode_b60": 5 * 206_274_048, "prefill_nc": 19_081_728}
-NCU_TRAFFIC_CAPTURED_AT = {"decode_b60": "split-KV kernel with a separate merge launch (before the in-kernel merge)",
+# (decode: 4 x a B=15 capture of the same kernel, traffic grows with the K/V bytes; prefill: a capture of the
+# workload itself).  A capture describes the kernel as it was when it was taken: "captured_at" says which.
+NCU_TRAFFIC_BYTES = {"decode_b60": 4 * 256_469_504, "prefill_nc": 19_081_728}
+NCU_TRAFFIC_CAPTURED_AT = {"decode_b60": "split-KV kernel with the merge inside, 120 workers (B=15 capture x 4)",
                            "prefill_nc": "two-tile tcgen05 kernel, region-C version"}
 
 
