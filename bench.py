@@ -11,6 +11,7 @@ Workloads (synthetic, seeded; shapes are the baseline configurations of this pat
                     against the single-GPU result and the CPU oracle
     decode_b60      GQA decode, B=60 per GPU, S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D]   (headline)
     decode_b60_strong  the same shape as ONE batch of 60 sequences split 60/30/15/8,7 across the ranks (strong scaling)
+    decode_step_rope   decode_b60 with the rotary embedding of the new token and the cache append inside the kernel
     decode_long     one sequence, S=1,048,576, Hq=64, Hkv=8, KV sharded by position across GPUs
                     (all-gather of per-GPU partials + LSE combine; strong scaling)
     prefill_nc      prefill forward, non-causal, B=1, S=4096, Hq=16, Hkv=1
@@ -178,6 +179,24 @@ def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
                   "global_batch": 60, "kv_seq_len": S, "sharding": "batch (no collective)",
                   "l2": "a rank's share at 8 GPUs (118-134 MB) is about the size of the 126 MB L2: the line says what "
                         "a decode step of this batch costs, not an HBM figure"}
+        host_in = [q, k, v]
+    elif wl == "decode_step_rope":
+        # a whole decoder step at the headline shape: rotary embedding of the new token's Q and K, cache append, attention
+        B, S, Hq, Hkv = (args.batch or 60), 4096, 128, 8
+        layout = ops.KV_BSHD
+        q, k, v = randn_bf16((B, Hq, 128)), randn_bf16((B, S, Hkv, 128)), randn_bf16((B, S, Hkv, 128))
+        k_new, v_new = randn_bf16((B, Hkv, 128)), randn_bf16((B, Hkv, 128))
+        out = torch.empty_like(q)
+        step_fn = lambda: ops.gqa_decode_rope_append(q, k_new, v_new, k, v, S, kv_layout=layout, out=out)  # noqa: E731
+        units_per_rank = decode_bytes(B, S, Hq, Hkv) + 4 * (B * Hkv * 128) * 2  # + new K/V read and appended
+        total_units = units_per_rank * world
+        metric, unit, scale_div, bound = "gqa_decode_achieved_hbm_tbps", "TB/s", 1e12, "hbm"
+        launches_per_step = 1
+        scaling = "weak"
+        config = {"workload": "decode_step_rope: rotary embedding of the new token + cache append + GQA decode in one "
+                              "kernel, B=%d per GPU, S=4096, Hq=128, Hkv=8, D=128, K/V [B,S,Hkv,D]" % B,
+                  "global_batch": B * world, "kv_seq_len": S, "sharding": "batch (no collective)",
+                  "l2": "inputs exceed the 126 MB L2; no flush needed"}
         host_in = [q, k, v]
     elif wl == "decode_b60":
         B, S, Hq, Hkv = (args.batch or 60), 4096, 128, 8
@@ -759,7 +778,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="all",
-                    choices=["all", "decode_b60", "decode_b60_strong", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
+                    choices=["all", "decode_b60", "decode_b60_strong", "decode_step_rope", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
                     help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")

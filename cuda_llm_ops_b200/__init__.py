@@ -14,6 +14,7 @@ from .flash_gqa import (  # noqa: F401
     device_status,
     gqa_combine,
     gqa_decode,
+    gqa_decode_rope_append,
     gqa_decode_sharded,
     launch_decode_flash_gqa_bf16_kernel,
     launch_flash_gqa_backward_bf16_kernel,

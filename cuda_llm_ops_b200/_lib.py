@@ -30,6 +30,8 @@ _SIGNATURES = {
     "cllo_gqa_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "cllo_gqa_decode_plan": (_i, [_i, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_i)]),
     "cllo_gqa_decode_bf16": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "cllo_gqa_decode_rope_append_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i,
+                                              _i, _i, _vp]),
     "cllo_gqa_combine_bf16": (_i, [_vp, _i, _vp, _ll, _i, _vp]),
     "cllo_gqa_exchange_combine_bf16": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _i, ctypes.c_uint, _vp,
                                             _i, _i, _i, _i, _vp]),

@@ -112,15 +112,18 @@ int cllo_gqa_decode_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, 
 struct KvMapCache {
     const void* k = nullptr;
     const void* v = nullptr;
-    int B = 0, S = 0, Hkv = 0, layout = -1;
+    int B = 0, S = 0, S_cap = 0, Hkv = 0, layout = -1;
     CUtensorMap tm_k, tm_v;
 };
 static thread_local KvMapCache t_kv_maps;
 
 static int decode_launch(const void* q, const void* k, const void* v, float scale, void* o, void* workspace,
                          size_t workspace_bytes, int B, int S, int Hq, int Hkv, int D, int kv_layout, int num_workers,
-                         float* partial_out, const shard::Params* sp, cudaStream_t st) {
+                         float* partial_out, const shard::Params* sp, cudaStream_t st,
+                         decode::RopeParams* rp = nullptr, int S_cap = 0) {
     if (!q || !k || !v || (!o && !partial_out)) return CLLO_E_BAD_ARG;
+    if (S_cap == 0) S_cap = S;
+    if (S_cap < S) return CLLO_E_BAD_ARG;
     const bool counters_zero = (kv_layout & CLLO_WS_COUNTERS_ZERO) != 0;
     kv_layout &= ~CLLO_WS_COUNTERS_ZERO;
     if (kv_layout != CLLO_KV_BSHD && kv_layout != CLLO_KV_BHSD) return CLLO_E_BAD_ARG;
@@ -146,24 +149,28 @@ static int decode_launch(const void* q, const void* k, const void* v, float scal
     p.kv_layout = kv_layout;
 
     KvMapCache& mc = t_kv_maps;
-    if (mc.k != k || mc.v != v || mc.B != B || mc.S != S || mc.Hkv != Hkv || mc.layout != kv_layout) {
+    if (mc.k != k || mc.v != v || mc.B != B || mc.S != S || mc.S_cap != S_cap || mc.Hkv != Hkv ||
+        mc.layout != kv_layout) {
         mc.layout = -1;
-        rc = decode::encode_kv_map(&mc.tm_k, k, B, S, Hkv, kv_layout);
+        rc = decode::encode_kv_map(&mc.tm_k, k, B, S, Hkv, kv_layout, S_cap);
         if (rc != CLLO_OK) return rc;
-        rc = decode::encode_kv_map(&mc.tm_v, v, B, S, Hkv, kv_layout);
+        rc = decode::encode_kv_map(&mc.tm_v, v, B, S, Hkv, kv_layout, S_cap);
         if (rc != CLLO_OK) return rc;
         mc.k = k;
         mc.v = v;
         mc.B = B;
         mc.S = S;
+        mc.S_cap = S_cap;
         mc.Hkv = Hkv;
         mc.layout = kv_layout;
     }
 
     if (!di->decode_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<false>,
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<false, false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<true>,
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<true, false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(decode::decode_splitkv_kernel<false, true>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBytes));
         di->decode_attr_set = true;
     }
@@ -171,11 +178,21 @@ static int decode_launch(const void* q, const void* k, const void* v, float scal
     // zero, so a caller that keeps a workspace for this library alone can vouch for them and save the memset node.
     if (plan.needs_merge && !(counters_zero && plan.counters_fixed))
         CLLO_CUDA_TRY(cudaMemsetAsync(static_cast<char*>(workspace) + plan.counter_offset, 0, plan.counter_bytes, st));
-    if (sp) {
-        decode::decode_splitkv_kernel<true><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p, *sp);
+    static const shard::Params no_shard = {};
+    static const decode::RopeParams no_rope = {};
+    if (rp) {
+        const long long row = decode::kD;
+        rp->tok_stride = kv_layout == CLLO_KV_BSHD ? row * Hkv : row;
+        rp->head_stride = kv_layout == CLLO_KV_BSHD ? row : row * S_cap;
+        rp->batch_stride = row * S_cap * Hkv;
+        decode::decode_splitkv_kernel<false, true><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p,
+                                                                                                      no_shard, *rp);
+    } else if (sp) {
+        decode::decode_splitkv_kernel<true, false><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p,
+                                                                                                      *sp, no_rope);
     } else {
-        shard::Params none = {};
-        decode::decode_splitkv_kernel<false><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v, p, none);
+        decode::decode_splitkv_kernel<false, false><<<p.W, decode::kThreads, decode::kSmemBytes, st>>>(mc.tm_k, mc.tm_v,
+                                                                                                       p, no_shard, no_rope);
     }
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
@@ -198,6 +215,26 @@ int cllo_gqa_decode_sharded_bf16(const void* q, const void* k, const void* v, fl
     if (rc != CLLO_OK) return rc;
     return decode_launch(q, k, v, scale, o, workspace, workspace_bytes, B, S_local, Hq, Hkv, D, kv_layout,
                          num_workers, nullptr, &sp, static_cast<cudaStream_t>(stream));
+}
+
+int cllo_gqa_decode_rope_append_bf16(const void* q, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                                     const int* positions, float rope_base, float scale, void* o, void* workspace,
+                                     size_t workspace_bytes, int B, int S, int S_capacity, int Hq, int Hkv, int D,
+                                     int kv_layout, int num_workers, void* stream) {
+    if (!k_new || !v_new || !o) return CLLO_E_BAD_ARG;
+    if (!aligned_to(k_new, 8) || !aligned_to(v_new, 8)) return CLLO_E_BAD_ARG;
+    if (!(rope_base > 0.f) || D != decode::kD) return D != decode::kD ? CLLO_E_UNSUPPORTED : CLLO_E_BAD_ARG;
+    decode::RopeParams rp = {};
+    rp.k_new = static_cast<const __nv_bfloat16*>(k_new);
+    rp.v_new = static_cast<const __nv_bfloat16*>(v_new);
+    rp.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    rp.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    rp.positions = positions;
+    // the inverse frequencies come from the host's powf, as in cllo_rope_bf16 with hidden = head_dim
+    const float inv_d = 1.0f / static_cast<float>(decode::kD);
+    for (int i = 0; i < decode::kD / 2; ++i) rp.inv_freq[i] = std::pow(rope_base, -2.0f * static_cast<float>(i) * inv_d);
+    return decode_launch(q, k_cache, v_cache, scale, o, workspace, workspace_bytes, B, S, Hq, Hkv, D, kv_layout,
+                         num_workers, nullptr, nullptr, static_cast<cudaStream_t>(stream), &rp, S_capacity);
 }
 
 size_t cllo_gqa_shard_gather_bytes(int world, int B, int Hq, int D) {

@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "gqa_shard.cuh"
 #include "host_util.cuh"
+#include "rope.cuh"
 
 namespace cllo {
 namespace decode {
@@ -78,6 +79,20 @@ struct Params {
     long long T;  // total tiles
 };
 
+// Decode step with the rotary embedding and the cache append folded in (kRope): the new token's query is rotated as
+// its fragments are loaded, and the worker that owns the last KV tile of a (batch, kv head) unit puts the rotated new
+// key and the new value into that tile in shared memory -- and into the cache in global memory for later steps --
+// before it uses the tile.  A separate rotary pass over Q and K and a separate append kernel disappear from the step.
+struct RopeParams {
+    const __nv_bfloat16* k_new;  // [B,Hkv,D] un-rotated key of the new token
+    const __nv_bfloat16* v_new;  // [B,Hkv,D]
+    __nv_bfloat16* k_cache;      // the K/V the tensor maps read; row S-1 of every (batch, kv head) is written here
+    __nv_bfloat16* v_cache;
+    const int* positions;        // nullable, [B]: rotary position of the new token; default S-1
+    long long batch_stride, head_stride, tok_stride;  // of the caches, in elements
+    float inv_freq[kD / 2];
+};
+
 __host__ __device__ __forceinline__ long long worker_lo(long long w, long long T, long long W) {
     return (w * T) / W;
 }
@@ -86,10 +101,10 @@ __host__ __device__ __forceinline__ long long worker_of_tile(long long t, long l
     return ((t + 1) * W - 1) / T;
 }
 
-template <bool kSharded>
+template <bool kSharded, bool kRope>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const Params p, const shard::Params sp) {
+                      const Params p, const shard::Params sp, const RopeParams rp) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -196,6 +211,26 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const int rows = (p.G - gblk * kRows) < kRows ? (p.G - gblk * kRows) : kRows;
         const long long head0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * p.G + gblk * kRows;
 
+        // rotary table of this unit's batch element: (cos, sin) of position * inv_freq for the 64 pairs of a head.
+        // It lives in the exchange buffer, which is idle until the end-of-unit merge (whose first barrier every warp
+        // reaches only after it has finished reading the table).
+        float2* rope_tab = reinterpret_cast<float2*>(xchg);
+        if (kRope) {
+            named_bar_sync(1, kConsumerWarps * 32);  // the previous unit's merge has finished with the buffer
+            if (threadIdx.x < kD / 2) {
+                const int pos = rp.positions ? rp.positions[b] : p.S - 1;
+                float sn, cs;
+                rope::sincos_accurate(static_cast<float>(pos) * rp.inv_freq[threadIdx.x], sn, cs);
+                rope_tab[threadIdx.x] = make_float2(cs, sn);
+            }
+            named_bar_sync(1, kConsumerWarps * 32);
+        }
+        auto rotate_pair = [&](uint32_t w, int pair) {
+            const float2 cs = rope_tab[pair];
+            const float even = __uint_as_float(w << 16), odd = __uint_as_float(w & 0xffff0000u);
+            return pack_bf16x2(even * cs.x - odd * cs.y, even * cs.y + odd * cs.x);
+        };
+
         // Q fragments of this unit (A operand, rows = query heads of the group, zero padded)
         uint32_t qf[8][4];
         {
@@ -208,6 +243,12 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 qf[ks][1] = v1 ? __ldg(q1 + ks * 8 + tig) : 0u;
                 qf[ks][2] = v0 ? __ldg(q0 + ks * 8 + tig + 4) : 0u;
                 qf[ks][3] = v1 ? __ldg(q1 + ks * 8 + tig + 4) : 0u;
+                if (kRope) {  // a 32-bit word is one (even, odd) pair of the head dimension
+                    qf[ks][0] = rotate_pair(qf[ks][0], ks * 8 + tig);
+                    qf[ks][1] = rotate_pair(qf[ks][1], ks * 8 + tig);
+                    qf[ks][2] = rotate_pair(qf[ks][2], ks * 8 + tig + 4);
+                    qf[ks][3] = rotate_pair(qf[ks][3], ks * 8 + tig + 4);
+                }
             }
         }
 
@@ -229,6 +270,30 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             const uint32_t vb = kb + 2 * kHalfBytes;
             const int tok0 = static_cast<int>(t - unit_lo) * kTok + sub * kSubTok;  // first token of this warp
             const int valid = p.S - tok0;  // tokens of this warp's 16 that exist (may be <= 0 or >= 16)
+
+            if (kRope && valid > 0 && valid <= kSubTok) {
+                // the new token (position S-1) is one of this warp's 16 rows, and only this warp reads them: put its
+                // rotated key and its value into the tile (lane = 4 consecutive dims = 2 pairs), and into the cache
+                const uint32_t srow = static_cast<uint32_t>(sub * kSubTok + valid - 1);
+                const int d0 = lane * 4;
+                const long long src = (static_cast<long long>(b) * p.Hkv + kvh) * kD + d0;
+                uint2 kn = *reinterpret_cast<const uint2*>(rp.k_new + src);
+                const uint2 vn = *reinterpret_cast<const uint2*>(rp.v_new + src);
+                kn.x = rotate_pair(kn.x, lane * 2);
+                kn.y = rotate_pair(kn.y, lane * 2 + 1);
+                const uint32_t off = static_cast<uint32_t>(d0 >> 6) * kHalfBytes + srow * 128u +
+                                     (((static_cast<uint32_t>(d0 & 63) >> 3) ^ (srow & 7u)) << 4) +
+                                     static_cast<uint32_t>(d0 & 7) * 2u;
+                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(kb + off), "r"(kn.x), "r"(kn.y) : "memory");
+                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(vb + off), "r"(vn.x), "r"(vn.y) : "memory");
+                if (gblk == 0) {
+                    const long long dst = static_cast<long long>(b) * rp.batch_stride + kvh * rp.head_stride +
+                                          static_cast<long long>(p.S - 1) * rp.tok_stride + d0;
+                    *reinterpret_cast<uint2*>(rp.k_cache + dst) = kn;
+                    *reinterpret_cast<uint2*>(rp.v_cache + dst) = vn;
+                }
+                __syncwarp();
+            }
 
             if (valid > 0) {
                 // ---- S = Q K^T  (16 heads x 16 tokens) ----
@@ -539,7 +604,8 @@ static int make_plan(int B, int S, int Hq, int Hkv, int D, int num_workers, int 
     return CLLO_OK;
 }
 
-static int encode_kv_map(CUtensorMap* map, const void* base, int B, int S, int Hkv, int kv_layout) {
+// S_cap: the token capacity the cache was allocated with (>= S); rows [S, S_cap) are outside the map and read as zero
+static int encode_kv_map(CUtensorMap* map, const void* base, int B, int S, int Hkv, int kv_layout, int S_cap) {
     const uint64_t row = static_cast<uint64_t>(kD) * 2;
     uint64_t dims[4], strides[3];
     uint32_t box[4];
@@ -556,12 +622,12 @@ static int encode_kv_map(CUtensorMap* map, const void* base, int B, int S, int H
         dims[1] = static_cast<uint64_t>(S);
         dims[2] = static_cast<uint64_t>(Hkv);
         strides[0] = row;
-        strides[1] = row * S;
+        strides[1] = row * S_cap;
         box[1] = kTok;
         box[2] = 1;
     }
     dims[3] = static_cast<uint64_t>(B);
-    strides[2] = row * static_cast<uint64_t>(S) * Hkv;
+    strides[2] = row * static_cast<uint64_t>(S_cap) * Hkv;
     box[3] = 1;
     return encode_bf16_4d(map, base, dims, strides, box);
 }

@@ -144,6 +144,47 @@ def gqa_decode_sharded(q, k_local, v_local, peer_gather, peer_flags, rank, world
     return out
 
 
+def gqa_decode_rope_append(q, k_new, v_new, k_cache, v_cache, seq_len, positions=None, rope_base=10000.0, scale=None,
+                           kv_layout=KV_BHSD, out=None, num_workers=0, workspace=None):
+    """One decode step with rotary embedding and cache append inside the attention kernel
+    (``cllo_gqa_decode_rope_append_bf16``).
+
+    q [B,Hq,D], k_new / v_new [B,Hkv,D]: the new token, un-rotated.  k_cache / v_cache: [B,S_cap,Hkv,D] (KV_BSHD) or
+    [B,Hkv,S_cap,D] (KV_BHSD) holding ``seq_len - 1`` earlier tokens; the call writes the rotated new key and the new
+    value at position ``seq_len - 1`` (in place) and returns the attention output over ``seq_len`` positions.
+    ``positions`` (int32 [B], optional) gives the rotary position per sequence; default ``seq_len - 1``.
+    """
+    B, S_cap, Hq, Hkv, D = _decode_shapes(q, k_cache, v_cache, kv_layout)
+    for name, t in (("k_new", k_new), ("v_new", v_new)):
+        _require_cuda_bf16(name, t)
+        if tuple(t.shape) != (B, Hkv, D) or not t.is_contiguous():
+            raise ValueError("%s must be contiguous [B,Hkv,D]" % name)
+    if not 1 <= seq_len <= S_cap:
+        raise ValueError("seq_len must lie in [1, cache capacity]")
+    if positions is not None:
+        if positions.dtype != torch.int32 or tuple(positions.shape) != (B,) or not positions.is_cuda \
+                or not positions.is_contiguous():
+            raise ValueError("positions must be a contiguous CUDA int32 tensor [B]")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty_like(q)
+    if out.dtype != torch.bfloat16 or out.shape != q.shape or not out.is_contiguous():
+        raise ValueError("Output tensor must be contiguous bf16 of q's shape")
+    with torch.cuda.device(q.device):
+        nbytes = decode_workspace_bytes(B, seq_len, Hq, Hkv, D, num_workers)
+        if workspace is None:
+            workspace = _workspace(q.device, nbytes)
+            kv_layout |= _lib.WS_COUNTERS_ZERO
+        rc = _lib.load().cllo_gqa_decode_rope_append_bf16(
+            q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            positions.data_ptr() if positions is not None else None, float(rope_base), float(scale), out.data_ptr(),
+            workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, seq_len, S_cap, Hq, Hkv, D,
+            kv_layout, num_workers, _stream_ptr())
+    _lib.check(rc, "cllo_gqa_decode_rope_append_bf16")
+    return out
+
+
 def set_exchange_wait_limit(sm_cycles):
     """Upper bound, in SM clock cycles, of one wait for a peer in the sharded decode (<= 0: the default, ~1 s)."""
     _lib.check(_lib.load().cllo_set_exchange_wait_limit(int(sm_cycles)), "cllo_set_exchange_wait_limit")

@@ -86,6 +86,24 @@ int cllo_gqa_decode_bf16(const void* q, const void* k, const void* v, float scal
                          int B, int S, int Hq, int Hkv, int D,
                          int kv_layout, int num_workers, float* partial_out, void* stream);
 
+/*
+ * One decode step with the rotary embedding and the KV-cache append folded into the attention kernel.
+ * Stands in for the sequence RopeBf16Kernel on the new token's Q and K (src/cplusplus/RoPE/rope_kernel.cu:33-107,
+ * hidden = head_dim: interleaved pairs (2i, 2i+1) of each head rotated by position * base^(-2i/D)), a cache append,
+ * and decode_flash_gqa_bf16_kernel -- three passes upstream, one kernel here:
+ *   q [B,Hq,D] and k_new, v_new [B,Hkv,D]: the new token, un-rotated;
+ *   k_cache, v_cache: the caches in kv_layout with a token capacity of S_capacity >= S ([B,S_capacity,Hkv,D] or
+ *       [B,Hkv,S_capacity,D]); positions [0, S-1) hold earlier tokens (keys already rotated).  The call writes the
+ *       rotated k_new and v_new into position S-1 and attends over positions [0, S);
+ *   positions (device, nullable): [B] rotary position of the new token per sequence; NULL = S-1 for all;
+ *   everything else as cllo_gqa_decode_bf16.  The query is rotated as it is loaded; it is not written back.
+ */
+int cllo_gqa_decode_rope_append_bf16(const void* q, const void* k_new, const void* v_new,
+                                     void* k_cache, void* v_cache, const int* positions, float rope_base,
+                                     float scale, void* o, void* workspace, size_t workspace_bytes,
+                                     int B, int S, int S_capacity, int Hq, int Hkv, int D,
+                                     int kv_layout, int num_workers, void* stream);
+
 /* How a decode call would be cut up: plan[0] = workers actually launched, plan[1] = KV tiles per
  * (batch, kv head, 16-query-head block), plan[2..3] = total tiles (low, high 32 bits), plan[4] = 1 if some
  * head's share is cut between workers (partials are merged), plan[5] = tokens per tile.  Host-only arithmetic; sm_count <= 0 means "ask the device". */
