@@ -403,9 +403,10 @@ def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
     for _ in range(max(warmup, 3)):
         step_fn()
     barrier()
-    if wl == "decode_long" and world > 1 and dec.exchange in ("peer", "fused") and not args.no_graph:
-        # a step (counters' memset + the fused decode/exchange kernel) replayed from a CUDA graph: at ~100 us
-        # per step on 8 GPUs, host launch jitter between the ranks otherwise shows up as waiting in the exchange
+    if wl == "decode_long" and world > 1 and dec.exchange == "peer" and not args.no_graph:
+        # the two kernels of a step (decode, exchange) replayed from a CUDA graph: at ~100 us per step on 8 GPUs,
+        # host launch jitter between the ranks otherwise shows up as waiting in the exchange.  (The fused form is
+        # one kernel per step and is launched directly: measured 2 us faster than replaying a one-node graph.)
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
