@@ -34,8 +34,19 @@ def _stream_ptr():
     return torch.cuda.current_stream().cuda_stream
 
 
+_ws_bytes_cache = {}
+
+
 def decode_workspace_bytes(B, S, Hq, Hkv, D=HEAD_DIM, num_workers=0):
-    return int(_lib.load().cllo_gqa_decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers))
+    # asked on every decode call: remembered per shape (and device, whose SM count enters the library's choice)
+    key = (B, S, Hq, Hkv, D, num_workers, torch.cuda.current_device() if torch.cuda.is_available() else -1)
+    n = _ws_bytes_cache.get(key)
+    if n is None:
+        n = int(_lib.load().cllo_gqa_decode_workspace_bytes(B, S, Hq, Hkv, D, num_workers))
+        if len(_ws_bytes_cache) > 4096:
+            _ws_bytes_cache.clear()
+        _ws_bytes_cache[key] = n
+    return n
 
 
 def _workspace(device, nbytes):
