@@ -302,7 +302,7 @@ def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
     elif wl == "prefill_chunk":
         # a chunk of 64 new query tokens against 8192 cached ones (chunked prefill / speculative decoding): the
         # one-tile kernel, two heads of a group sharing each 128-row tile
-        B, Sq, Skv, Hq, Hkv = 8, 64, 8192, 32, 4
+        B, Sq, Skv, Hq, Hkv = (args.batch or 8), 64, 8192, 32, 4
         q, k, v = randn_bf16((B, Hq, Sq, 128)), randn_bf16((B, Hkv, Skv, 128)), randn_bf16((B, Hkv, Skv, 128))
         out = torch.empty_like(q)
         lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
@@ -782,7 +782,8 @@ def main():
                     choices=["all", "decode_b60", "decode_b60_strong", "decode_step_rope", "decode_long", "prefill_nc", "prefill_causal", "swa", "backward", "rope", "sgqa", "mla", "prefill_chunk"])
     ap.add_argument("--layout", default="bshd", choices=["bshd", "bhsd"])
     ap.add_argument("--batch", type=int, default=0,
-                    help="decode_b60 only: override the per-GPU batch (small cases for profiler captures)")
+                    help="decode_b60 / prefill_chunk: override the per-GPU batch (small cases for profiler captures; "
+                         "prefill_chunk at a batch of 1-4 runs with the kv range shared out among blocks)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "peer", "nccl"],
                     help="decode_long on several GPUs: how the per-GPU partials are exchanged")
     ap.add_argument("--kv-len", type=int, default=0,

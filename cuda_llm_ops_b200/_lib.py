@@ -41,6 +41,8 @@ _SIGNATURES = {
     "cllo_gqa_shard_flag_bytes": (_sz, [_i]),
     "cllo_set_exchange_wait_limit": (_i, [_ll]),
     "cllo_gqa_prefill_fwd_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "cllo_gqa_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "cllo_gqa_prefill_fwd_ws_bf16": (_i, [_vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "cllo_gqa_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp]),
     "cllo_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _f, _vp]),

@@ -256,8 +256,9 @@ int cllo_gqa_combine_bf16(const float* partials, int nsplit, void* o, long long 
     if (!partials || !o || nsplit <= 0 || rows <= 0) return CLLO_E_BAD_ARG;
     if (D != decode::kD) return CLLO_E_UNSUPPORTED;
     if (rows > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
-    decode::combine_rows_kernel<<<static_cast<unsigned>(rows), decode::kD, 0, static_cast<cudaStream_t>(stream)>>>(
-        partials, nsplit, rows, static_cast<__nv_bfloat16*>(o));
+    decode::combine_rows_kernel<<<static_cast<unsigned>((rows + decode::kCombineRows - 1) / decode::kCombineRows),
+                                  decode::kCombineRows * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        partials, nsplit, rows, static_cast<__nv_bfloat16*>(o), nullptr);
     CLLO_CUDA_TRY(cudaGetLastError());
     return CLLO_OK;
 }
@@ -269,14 +270,53 @@ int cllo_gqa_exchange_combine_bf16(const float* local_partial, void* const* peer
                             static_cast<cudaStream_t>(stream));
 }
 
-int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
-                              float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+// The forward with an optional workspace.  A chunk of query tokens against a long cache (non-causal, fewer than 256
+// rows per head) runs on the two-tile kernel with the heads of a group as extra rows, and -- given a workspace -- with
+// the kv range cut into shares for different blocks when the blocks would otherwise not fill the GPU.
+static int prefill_dispatch(const void* q, const void* k, const void* v, float scale, int causal, void* o, float* lse,
+                            void* workspace, size_t workspace_bytes, int B, int Sq, int Skv, int Hq, int Hkv, int D,
+                            cudaStream_t stream) {
+    if (D == 128 && B > 0 && Sq > 0 && Skv > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && !causal) {
+        DeviceInfo* di = nullptr;
+        if (current_device_info(&di) == CLLO_OK) {
+            prefill::Layout L = prefill::choose_layout(B, Sq, Skv, Hq, Hkv, causal, 0, nullptr, di->sm_count,
+                                                       workspace != nullptr);
+            if (L.n_split > 1 && workspace_bytes < L.ws_bytes)
+                L = prefill::choose_layout(B, Sq, Skv, Hq, Hkv, causal, 0, nullptr, di->sm_count, false);
+            const long long blocks = static_cast<long long>(B) * L.Hq_eff * ((L.Sq_eff + 255) / 256) * L.n_split;
+            // worth it when the kv range is shared out, or when the merged rows alone give the GPU enough blocks
+            if (L.n_split > 1 || (L.merged && blocks >= di->sm_count))
+                return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D, stream, &L,
+                                       workspace);
+        }
+    }
     // all query rows in one 128-row tile (chunked prefill, a few decode tokens): the one-tile kernel, which does not
     // spend half its work on an empty second tile
     if (D == 128 && Sq > 0 && Sq <= 128)
-        return mla::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D, D, static_cast<cudaStream_t>(stream));
-    return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D,
-                           static_cast<cudaStream_t>(stream));
+        return mla::launch(q, k, v, scale, causal, o, lse, B, Sq, Skv, Hq, Hkv, D, D, stream);
+    return prefill::launch(q, k, v, scale, causal, 0, nullptr, o, lse, B, Sq, Skv, Hq, Hkv, D, stream);
+}
+
+int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
+                              float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream) {
+    return prefill_dispatch(q, k, v, scale, causal, o, lse, nullptr, 0, B, Sq, Skv, Hq, Hkv, D,
+                            static_cast<cudaStream_t>(stream));
+}
+
+size_t cllo_gqa_prefill_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv, int causal) {
+    if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return 0;
+    int sm = 0;
+    DeviceInfo* di = nullptr;
+    if (current_device_info(&di) == CLLO_OK) sm = di->sm_count;
+    if (sm <= 0) sm = 256;  // no device visible: the largest cut any current part would ask for
+    return prefill::choose_layout(B, Sq, Skv, Hq, Hkv, causal, 0, nullptr, sm, true).ws_bytes;
+}
+
+int cllo_gqa_prefill_fwd_ws_bf16(const void* q, const void* k, const void* v, float scale, int causal, void* o,
+                                 float* lse, void* workspace, size_t workspace_bytes, int B, int Sq, int Skv, int Hq,
+                                 int Hkv, int D, void* stream) {
+    return prefill_dispatch(q, k, v, scale, causal, o, lse, workspace, workspace_bytes, B, Sq, Skv, Hq, Hkv, D,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int cllo_rope_bf16(const void* input, void* output, int B, int S, int hidden, float base, void* stream) {

@@ -509,25 +509,39 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
 }
 
-// Public merge of caller-provided partials [nsplit][rows][D+2] -> bf16 [rows][D].  One row per block.
-__global__ void __launch_bounds__(kD) combine_rows_kernel(const float* __restrict__ partials, int nsplit,
-                                                          long long rows, __nv_bfloat16* __restrict__ o) {
-    const long long r = blockIdx.x;
-    const int d = threadIdx.x;
+// Public merge of caller-provided partials [nsplit][rows][D+2] -> bf16 [rows][D] (and, when asked, the rows'
+// log-sum-exp m + log l in natural-log units).  One warp per row (lane = 4 columns), eight rows per block.
+constexpr int kCombineRows = 8;
+__global__ void __launch_bounds__(kCombineRows * 32) combine_rows_kernel(const float* __restrict__ partials, int nsplit,
+                                                                         long long rows, __nv_bfloat16* __restrict__ o,
+                                                                         float* __restrict__ lse) {
+    const long long r = static_cast<long long>(blockIdx.x) * kCombineRows + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int c4 = (threadIdx.x & 31) * 4;
     float mstar = -INFINITY;
     for (int i = 0; i < nsplit; ++i) {
-        const float* row = partials + (static_cast<long long>(i) * rows + r) * kPW;
-        if (row[kD + 1] > 0.f) mstar = fmaxf(mstar, row[kD]);
+        const float2 ml = *reinterpret_cast<const float2*>(partials + (static_cast<long long>(i) * rows + r) * kPW + kD);
+        if (ml.y > 0.f) mstar = fmaxf(mstar, ml.x);
     }
-    float acc = 0.f, lsum = 0.f;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, lsum = 0.f;
     for (int i = 0; i < nsplit; ++i) {
         const float* row = partials + (static_cast<long long>(i) * rows + r) * kPW;
-        const float l = row[kD + 1];
-        const float wgt = l > 0.f ? __expf(row[kD] - mstar) : 0.f;
-        acc += wgt * row[d];
-        lsum += wgt * l;
+        const float2 ml = *reinterpret_cast<const float2*>(row + kD);
+        const float wgt = ml.y > 0.f ? __expf(ml.x - mstar) : 0.f;
+        const float2 x = *reinterpret_cast<const float2*>(row + c4);
+        const float2 y = *reinterpret_cast<const float2*>(row + c4 + 2);
+        a0 += wgt * x.x;
+        a1 += wgt * x.y;
+        a2 += wgt * y.x;
+        a3 += wgt * y.y;
+        lsum += wgt * ml.y;
     }
-    o[r * kD + d] = __float2bfloat16(lsum > 0.f ? acc / lsum : 0.f);
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    uint2 pk;
+    pk.x = pack_bf16x2(a0 * inv, a1 * inv);
+    pk.y = pack_bf16x2(a2 * inv, a3 * inv);
+    *reinterpret_cast<uint2*>(o + r * kD + c4) = pk;
+    if (lse && c4 == 0) lse[r] = lsum > 0.f ? mstar + logf(lsum) : -INFINITY;
 }
 
 // ---------------------------------------------------------------------------------------------

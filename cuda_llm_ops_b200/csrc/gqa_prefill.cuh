@@ -25,6 +25,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "gqa_decode.cuh"
 #include "host_util.cuh"
 
 #include <cstdlib>
@@ -81,6 +82,10 @@ struct Params {
     int B, Sq, Skv, Hq, Hkv, G, causal, n_qp;
     int window;         // > 0: sliding window, a query sees kv in [q - (window - 1), q] (implies causal)
     const float* sink;  // nullable, [Hq]: per-head term added to the softmax denominator
+    // split-KV mode (n_split > 1): block (.., split) covers one share of the kv tiles and leaves, instead of O and
+    // lse, packed fp32 rows {un-normalised O[128], m (natural-log units), l} in part[split][B*Hq*Sq][130]
+    float* part;
+    int n_split;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
@@ -366,7 +371,9 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int qp = p.n_qp - 1 - static_cast<int>(id % p.n_qp);
     id /= p.n_qp;
     const int kvh = static_cast<int>(id % p.Hkv);
-    const int b = static_cast<int>(id / p.Hkv);
+    id /= p.Hkv;
+    const int b = static_cast<int>(id % p.B);
+    const int split = static_cast<int>(id / p.B);
     const int h = kvh * p.G + g;
     const int q0 = qp * (kTiles * kBM);
 
@@ -380,6 +387,11 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     int j_lo = 0;
     if (p.window > 0 && q0 - (p.window - 1) > 0) j_lo = (q0 - (p.window - 1)) / kBN;
     if (j_lo > j_hi - 1) j_lo = j_hi - 1;
+    if (p.n_split > 1) {  // this block's share of the tiles (the launcher makes every share non-empty)
+        const int len = (j_hi - j_lo + p.n_split - 1) / p.n_split;
+        j_lo += split * len;
+        j_hi = j_lo + len < j_hi ? j_lo + len : j_hi;
+    }
     const int n_kv = j_hi - j_lo;  // >= 1; the loops below count local tiles, tile j is global tile j_lo + j
 
     if (warp == 8 && lane == 0) {
@@ -770,6 +782,25 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float denom = l + ((p.sink && visible) ? sink * fast_exp2(-m) : 0.f);
         const float inv_l = visible ? 1.f / denom : 0.f;
         const bool row_ok = qi < p.Sq;
+        if (p.part) {
+            // split-KV: the un-normalised accumulator and (m, l) of this share, one packed fp32 row per query row
+            // (the share index is worked out again here rather than kept in a register through the kv loop)
+            const int share = static_cast<int>(blockIdx.x) / (p.G * p.n_qp * p.Hkv * p.B);
+            float* dst = p.part + ((static_cast<size_t>(share) * p.B + b) * p.Hq + h) * static_cast<size_t>(p.Sq) * 130 +
+                         static_cast<size_t>(qi) * 130;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float ov[32];
+                tmem_ld32_wait(o_addr + c * 32, ov);
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2)
+                        *reinterpret_cast<float2*>(dst + c * 32 + e) = make_float2(ov[e], ov[e + 1]);
+                }
+            }
+            if (row_ok) *reinterpret_cast<float2*>(dst + 128) = make_float2(m * kLn2, l);
+            tc_fence_before();
+        } else {
         // O goes out through shared memory and a bulk tensor store: written row by row from the threads, one
         // store instruction touches 32 different lines and the epilogue is bound by those transactions.  The Q
         // tile of this query tile is free (every MMA has retired) and has the layout the store expects: two
@@ -803,6 +834,7 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + qi] =
                 visible ? (m + log2f(denom)) * kLn2 : (p.sink ? logf(fmaxf(sink, 1.0e-9f)) : -INFINITY);
         tc_fence_before();
+        }
     }
 
     __syncthreads();
@@ -824,8 +856,72 @@ static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, in
     return encode_bf16_4d(map, basep, dims, strides, box);
 }
 
+// How a forward call is laid out.  Two things can be changed without changing the result, both only for the plain
+// (non-causal, no window, no sink) case:
+//   * the query heads of a group become extra query ROWS of their kv head (q [B,Hq,Sq,D] read as [B,Hkv,G*Sq,D] is
+//     the same memory) when one head alone does not fill a block's two tiles -- the heads of a group read the same
+//     K/V, so a block then streams each K/V tile once for 256 rows of several heads;
+//   * the kv range is cut into n_split shares handled by different blocks (flash-decoding), when there are fewer
+//     blocks than SMs and enough kv tiles; the shares' packed partials go to the workspace and
+//     decode::combine_rows_kernel merges them.  Needs a workspace of ws_bytes.
+struct Layout {
+    int Hq_eff, Sq_eff, n_split;
+    size_t ws_bytes;
+    bool merged;
+};
+// Blocks of the launch without any of that: one per (batch, head, 256 rows), or, for chunks of at most 128 rows, the
+// one-tile kernel's count (chunks of at most 64 rows share a tile among P heads of a group: rows rounded up to a
+// power of two R, P = min(128 / R, largest power of two dividing G)).
+static long long plain_block_count(int B, int Sq, int Hq, int Hkv) {
+    if (Sq > kBM) return static_cast<long long>(B) * Hq * ((Sq + kTiles * kBM - 1) / (kTiles * kBM));
+    const int G = Hq / Hkv;
+    int P = 1;
+    if (Sq <= 64) {
+        int R = 1;
+        while (R < Sq) R <<= 1;
+        P = kBM / R;
+        while (P > 1 && (G % P) != 0) P >>= 1;
+    }
+    return static_cast<long long>(B) * Hkv * (G / P);
+}
+
+static Layout choose_layout(int B, int Sq, int Skv, int Hq, int Hkv, int causal, int window, const float* sink,
+                            int sm_count, bool may_split) {
+    Layout L;
+    L.Hq_eff = Hq;
+    L.Sq_eff = Sq;
+    L.n_split = 1;
+    L.ws_bytes = 0;
+    L.merged = false;
+    if (causal || window > 0 || sink) return L;
+    const int G = Hq / Hkv;
+    if (G > 1 && Sq < kTiles * kBM && static_cast<long long>(G) * Sq > kBM) {
+        L.merged = true;
+        L.Hq_eff = Hkv;
+        L.Sq_eff = G * Sq;
+    }
+    const long long n_qp = (L.Sq_eff + kTiles * kBM - 1) / (kTiles * kBM);
+    const long long base = static_cast<long long>(B) * L.Hq_eff * n_qp;
+    const int tiles = (Skv + kBN - 1) / kBN;
+    // Measured: with the kv range shared out each K/V tile is read by fewer blocks, comes from HBM rather than L2 and
+    // the two-stage K/V pipeline stalls on it, and the shares' partials cost a second kernel -- so the cut pays only
+    // where the ordinary launch would leave most of the GPU idle.
+    if (may_split && base < sm_count && tiles >= 16 && 2 * plain_block_count(B, Sq, Hq, Hkv) < sm_count) {
+        long long want = sm_count / base;
+        if (want > tiles / 8) want = tiles / 8;  // a share of fewer than eight tiles is mostly start-up and drain
+        if (want > 16) want = 16;
+        if (want >= 2) {
+            const int len = static_cast<int>((tiles + want - 1) / want);
+            L.n_split = (tiles + len - 1) / len;  // every share non-empty
+            L.ws_bytes = static_cast<size_t>(L.n_split) * B * Hq * Sq * 130 * sizeof(float);
+        }
+    }
+    return L;
+}
+
 static int launch(const void* q, const void* k, const void* v, float scale, int causal, int window, const float* sink,
-                  void* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream) {
+                  void* o, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, cudaStream_t stream,
+                  const Layout* layout = nullptr, void* workspace = nullptr) {
     if (window < 0) return CLLO_E_BAD_ARG;
     // masked scores are +-infinity BEFORE the scale is folded into the exponent: a zero (or non-finite) scale would
     // turn them into NaN, so it is refused
@@ -840,6 +936,14 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     if (rc != CLLO_OK) return rc;
     if (di->cc_major != 10) return CLLO_E_UNSUPPORTED;
 
+    const long long rows_total = static_cast<long long>(B) * Hq * Sq;
+    int n_split = 1;
+    if (layout) {  // heads as rows and/or kv shares (see choose_layout); the memory is read the same way
+        Hq = layout->Hq_eff;
+        Sq = layout->Sq_eff;
+        n_split = layout->n_split;
+        if (n_split > 1 && (!workspace || !aligned_to(workspace, 16))) return CLLO_E_WORKSPACE;
+    }
     Params p;
     p.o = static_cast<__nv_bfloat16*>(o);
     p.lse = lse;
@@ -853,9 +957,11 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     p.causal = (causal || window > 0) ? 1 : 0;
     p.window = window;
     p.sink = sink;
+    p.part = n_split > 1 ? static_cast<float*>(workspace) : nullptr;
+    p.n_split = n_split;
     p.n_qp = (Sq + kTiles * kBM - 1) / (kTiles * kBM);
-    const long long blocks = static_cast<long long>(B) * Hq * p.n_qp;
-    if (blocks > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
+    const long long blocks = static_cast<long long>(B) * Hq * p.n_qp * n_split;
+    if (blocks > 0x7fffffffLL || rows_total > 0x7fffffffLL) return CLLO_E_UNSUPPORTED;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if ((rc = encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
@@ -875,6 +981,11 @@ static int launch(const void* q, const void* k, const void* v, float scale, int 
     const unsigned grid = static_cast<unsigned>(blocks);
     prefill_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
     CLLO_CUDA_TRY(cudaGetLastError());
+    if (n_split > 1) {
+        decode::combine_rows_kernel<<<static_cast<unsigned>((rows_total + decode::kCombineRows - 1) / decode::kCombineRows),
+                                      decode::kCombineRows * 32, 0, stream>>>(p.part, n_split, rows_total, p.o, lse);
+        CLLO_CUDA_TRY(cudaGetLastError());
+    }
     return CLLO_OK;
 }
 

@@ -49,13 +49,14 @@ def decode_workspace_bytes(B, S, Hq, Hkv, D=HEAD_DIM, num_workers=0):
     return n
 
 
-def _workspace(device, nbytes):
-    """A per-device scratch tensor, grown on demand (torch owns the memory).
+def _workspace(device, nbytes, kind="decode"):
+    """A per-device scratch tensor per kind of use, grown on demand (torch owns the memory).  The decode scratch is
+    kept apart from any other: its first 4 KB are arrival counters that the decode calls vouch for.
 
     It is shared by every call on that device that does not bring its own ``workspace``: calls issued on different
     streams that may overlap on the GPU must each pass their own.
     """
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    key = (kind, device.type, device.index if device.index is not None else torch.cuda.current_device())
     with _workspaces_lock:
         ws = _workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
@@ -335,10 +336,21 @@ def launch_flash_gqa_forward_bf16_kernel(q, k, v, scale=None, out=None, lse=None
             raise ValueError("LSE must be contiguous fp32")
         lse_b = lse.unsqueeze(0) if squeeze else lse
     with torch.cuda.device(qb.device):
-        rc = _lib.load().cllo_gqa_prefill_fwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), float(scale),
-                                                   1 if causal else 0, out_b.data_ptr(), lse_b.data_ptr(),
-                                                   batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
-                                                   _stream_ptr())
+        lib = _lib.load()
+        # a few query rows against a long cache: the library asks for scratch to share the kv range out among blocks
+        ws_bytes = 0 if causal else int(lib.cllo_gqa_prefill_workspace_bytes(batch, seqlen_q, seqlen_kv, q_heads,
+                                                                             num_kv_heads, 0))
+        if ws_bytes:
+            ws = _workspace(qb.device, ws_bytes, kind="prefill")
+            rc = lib.cllo_gqa_prefill_fwd_ws_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), float(scale), 0,
+                                                  out_b.data_ptr(), lse_b.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                  batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
+                                                  _stream_ptr())
+        else:
+            rc = lib.cllo_gqa_prefill_fwd_bf16(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), float(scale),
+                                               1 if causal else 0, out_b.data_ptr(), lse_b.data_ptr(),
+                                               batch, seqlen_q, seqlen_kv, q_heads, num_kv_heads, head_dim_qk,
+                                               _stream_ptr())
     _lib.check(rc, "cllo_gqa_prefill_fwd_bf16")
     if squeeze:
         return out_b.squeeze(0), lse_b.squeeze(0)

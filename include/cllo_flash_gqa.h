@@ -212,6 +212,20 @@ int cllo_gqa_prefill_fwd_bf16(const void* q, const void* k, const void* v, float
                               int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
 
 /*
+ * The same forward with a caller-owned workspace (no upstream counterpart: upstream's launcher has no scratch).
+ * A chunk of query tokens against a long cache -- non-causal, few query rows, few (batch, kv head) pairs -- gives
+ * too few thread blocks to fill the GPU; with a workspace of cllo_gqa_prefill_workspace_bytes(...) bytes (16-byte
+ * aligned, contents arbitrary) the call cuts the kv range into shares for different blocks and merges the shares'
+ * partials (flash-decoding; the merge is the combine kernel of cllo_gqa_combine_bf16).  The size query returns 0 when
+ * the shape would not be cut; workspace may then be NULL.  Results are those of cllo_gqa_prefill_fwd_bf16 up to
+ * fp32 summation order.
+ */
+size_t cllo_gqa_prefill_workspace_bytes(int B, int Sq, int Skv, int Hq, int Hkv, int causal);
+int cllo_gqa_prefill_fwd_ws_bf16(const void* q, const void* k, const void* v, float scale, int causal,
+                                 void* o, float* lse, void* workspace, size_t workspace_bytes,
+                                 int B, int Sq, int Skv, int Hq, int Hkv, int D, void* stream);
+
+/*
  * Sliding-window attention forward with a sink term (the mask variant of the prefill forward):
  * a query at position i sees kv positions [i - (window_size - 1), i]; the softmax denominator of head h
  * is sum(exp(s - m)) + sink_value[h] * exp(-m); rows without any visible key give zeros and

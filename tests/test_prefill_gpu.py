@@ -142,3 +142,50 @@ def test_long_causal_shape_at_full_size_sampled_rows():
             got_lse = lse[b:b + 1, :, r0:r0 + 8].cpu().numpy()
             ol.assert_parity(got_o, want_o[:, :, r0:r0 + 8], "sequence %d rows %d" % (b, r0))
             assert np.allclose(got_lse, want_lse[:, :, r0:r0 + 8], atol=LSE_TOL)
+
+
+# Query chunks against a long cache (non-causal): the heads of a group become extra rows of the two-tile kernel and,
+# with a workspace, the kv range is shared out among blocks and merged.  (B, Hq, Hkv, Sq, Skv)
+CHUNK_CASES = [
+    (2, 16, 2, 64, 4096),     # 8 heads x 64 rows = 512 rows per kv head, kv range cut four ways
+    (1, 8, 2, 100, 2500),     # rows 400..511 of the merged tile pair empty, ragged kv tail, two shares
+    (1, 4, 4, 200, 3000),     # no grouping: shares only
+    (1, 32, 1, 8, 6000),      # 32 heads x 8 rows = 256 rows, many shares
+    (32, 16, 2, 64, 1024),    # enough (batch, kv head) pairs to fill the GPU: merged rows, no shares
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv", CHUNK_CASES)
+def test_query_chunk_against_long_cache(B, Hq, Hkv, Sq, Skv):
+    import cuda_llm_ops_b200 as ops
+    from cuda_llm_ops_b200 import _lib
+    q = ol.randn_bf16((B, Hq, Sq, 128), 151)
+    k = ol.randn_bf16((B, Hkv, Skv, 128), 152)
+    v = ol.randn_bf16((B, Hkv, Skv, 128), 153)
+    want_o, want_lse = ol.prefill(q, k, v, SCALE, False)
+    # through the launcher (brings its own scratch) ...
+    got_o, got_lse = _run(q, k, v, False)
+    ol.assert_parity(got_o, want_o, "chunk, launcher")
+    assert np.allclose(got_lse, want_lse, atol=LSE_TOL), np.abs(got_lse - want_lse).max()
+    # ... through the C ABI with a caller-owned workspace of the size the library asks for, and without one
+    lib = _lib.load()
+    qd, kd, vd = to_dev(q), to_dev(k), to_dev(v)
+    need = int(lib.cllo_gqa_prefill_workspace_bytes(B, Sq, Skv, Hq, Hkv, 0))
+    for with_ws in (True, False):
+        o = torch.zeros((B, Hq, Sq, 128), dtype=torch.bfloat16, device="cuda")
+        lse = torch.zeros((B, Hq, Sq), dtype=torch.float32, device="cuda")
+        ws = torch.full((max(need, 16),), 0xFF, dtype=torch.uint8, device="cuda")  # NaN patterns: nothing may be read unwritten
+        rc = lib.cllo_gqa_prefill_fwd_ws_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), SCALE, 0, o.data_ptr(),
+                                              lse.data_ptr(), ws.data_ptr() if with_ws else None, need if with_ws else 0,
+                                              B, Sq, Skv, Hq, Hkv, 128, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ol.assert_parity(to_bits(o), want_o, "chunk, C ABI, workspace=%s" % with_ws)
+        assert np.allclose(lse.cpu().numpy(), want_lse, atol=LSE_TOL)
+    # a workspace that is too small is simply not used
+    rc = lib.cllo_gqa_prefill_fwd_ws_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), SCALE, 0, o.data_ptr(),
+                                          lse.data_ptr(), ws.data_ptr(), 16, B, Sq, Skv, Hq, Hkv, 128, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ol.assert_parity(to_bits(o), want_o, "chunk, C ABI, tiny workspace")
+    assert_clean_status()
