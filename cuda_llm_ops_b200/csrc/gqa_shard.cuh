@@ -35,7 +35,7 @@ struct Params {
     long long rows_total;  // B * Hq
     long long wait_limit;  // SM cycles a flag wait may take
     int rank, world, units;
-    unsigned epoch;        // 0: take the step number from the launch-ticket word
+    unsigned epoch;        // 0: take the step number from the completion counter
 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {

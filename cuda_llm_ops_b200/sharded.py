@@ -46,7 +46,7 @@ class _PeerBuffers:
     """Gather slots and flag words in memory that every rank of the node can address (torch symmetric memory).
 
     Layout per rank as ``include/cllo_flash_gqa.h`` describes it: [2 parities][world][rows][D+2] fp32 gather
-    slots, then [world][CLLO_SHARD_MAX_UNITS] uint32 flag words and one launch-ticket word, all zero at first.
+    slots, then [world][CLLO_SHARD_MAX_UNITS] uint32 flag words and one completion counter, all zero at first.
     """
 
     def __init__(self, group, B, Hq, device):
