@@ -391,12 +391,10 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 sum2 = add2(sum2, pk2(p0, p1));
                 pk[e] = pack_bf16x2(p0, p1);
             }
-            // P[s] still feeds O += P(j-2) V(j-2) until that product has retired
-            if (j >= 2) {
-                mbar_wait(bar_pv_done(s), static_cast<uint32_t>((j - 2) >> 1) & 1u, abort_flag, SITE_MLA_PV, j);
-                __syncwarp();
-                tc_fence_after();
-            }
+            // P[s] fed O += P(j-2) V(j-2); that product has retired: S(j), whose arrival this step began by waiting
+            // for, was issued behind it in the same run, the tensor pipe works in order, and the commit that announced
+            // S(j) covers everything issued before it.  (A look at pv_done here costs this thread, which is the
+            // critical path of the kernel, 300-600 cycles of shared-memory round trip per step.)
             const uint32_t p_addr = tmem_base + lane_base + kColP + s * 64;
             tmem_st32(p_addr, *reinterpret_cast<const uint32_t(*)[32]>(&pk[0]));
             tmem_st32(p_addr + 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[32]));
