@@ -60,14 +60,7 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
     return d;
 }
 
-constexpr int kThreads = 320;  // warps 0-7 element-wise (row x half of the columns), 8 TMA, 9 MMA
-constexpr int kStages = 2;
-constexpr int kSmemFixed = 2 * kTileBytes;                      // dQ kernel: Q, dO;  dK/dV kernel: K, V
-constexpr int kSmemStream = kSmemFixed;                         // then [stage][2 tiles]
-constexpr int kSmemVec = kSmemStream + kStages * 2 * kTileBytes;  // dK/dV kernel: lse/D of the query tile, [2][2][128]
-constexpr int kSmemBar = kSmemVec + 2 * 2 * 128 * 4;
-constexpr int kNumBars = 12;
-constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+constexpr int kThreads = 320;  // warps 0-7 element-wise, 8 TMA, 9 MMA
 
 enum : int {
     SITE_BWD_FIXED = 40,
@@ -115,29 +108,6 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (lane == 0) delta[row] = acc;
-}
-
-struct Bars {
-    uint32_t base;
-    __device__ uint32_t fixed_full() const { return base; }
-    __device__ uint32_t stream_full(int s) const { return base + 8 * (1 + s); }
-    __device__ uint32_t stream_empty(int s) const { return base + 8 * (3 + s); }
-    __device__ uint32_t aux_empty(int s) const { return base + 8 * (5 + s); }  // dQ kernel: V stage released early
-    __device__ uint32_t s_full() const { return base + 8 * 7; }
-    __device__ uint32_t ds_full() const { return base + 8 * 8; }
-    __device__ uint32_t drain() const { return base + 8 * 9; }
-};
-
-__device__ __forceinline__ void init_bars(const Bars& bars) {
-    mbar_init(bars.fixed_full(), 1);
-    for (int s = 0; s < kStages; ++s) {
-        mbar_init(bars.stream_full(s), 1);
-        mbar_init(bars.stream_empty(s), 1);
-        mbar_init(bars.aux_empty(s), 1);
-    }
-    mbar_init(bars.s_full(), 1);
-    mbar_init(bars.ds_full(), 2 * kBM);
-    mbar_init(bars.drain(), 1);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -455,20 +425,125 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
 }
 
+// tcgen05.mma / commit issued by the lanes whose `leader` is non-zero while the WHOLE warp runs the surrounding code:
+// the operands (descriptor words, tensor-memory addresses) are then warp-uniform values that the compiler keeps in
+// uniform registers.  Under an `if (lane == 0)` they live in ordinary registers and every MMA pays several
+// register-to-uniform moves in the issuing thread -- measured here: 75-95 cycles per MMA issued, against 48-64 that
+// the tensor pipe needs.
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ss_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                uint32_t hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                uint32_t hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(leader)
+        : "memory");
+}
+
+// Four S-type MMAs (both operands in shared memory, k steps 32 bytes apart, all accumulating) issued by the leader
+// lane, behind a look at an mbarrier that every lane takes at its own barrier and reads only after the fourth MMA,
+// so that the round trip of the look is covered by the MMAs.
+__device__ __forceinline__ uint32_t tc_ss4_run_after_look(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                          uint32_t idesc, uint32_t leader, uint32_t look_bar,
+                                                          uint32_t look_parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pt, q, w;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 a, b;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 w, [%7], %8;\n\t"
+        "mov.b64 da, {%2, %4};\n\t mov.b64 db, {%3, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 2;\n\t add.u32 b, %3, 2;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 4;\n\t add.u32 b, %3, 4;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 6;\n\t add.u32 b, %3, 6;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "selp.u32 %0, 1, 0, w;\n\t"
+        "}"
+        : "=r"(seen)
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(leader), "r"(look_bar), "r"(look_parity)
+        : "memory");
+    return seen;
+}
+
 // ------------------------------------------------------------------------------------------------
 // dK, dV
 // ------------------------------------------------------------------------------------------------
+// A step is 64 query rows of one head against the block's 128 kv rows.  Steps alternate between two element-wise
+// groups of 128 threads (group = step parity), each with its own 64-column halves of S^T and dP^T in tensor memory
+// and its own pair of barriers, so the products of one group's steps run while the other group forms P^T and dS^T:
+//   MMA thread   S^T,dP^T(0) | S^T,dP^T(1) | wait dS(0): dV,dK(0), S^T,dP^T(2) | wait dS(1): dV,dK(1), S^T,dP^T(3) | ...
+//   group 0      ............. P^T,dS^T(0) ............................ P^T,dS^T(2) ...
+//   group 1      ........................... P^T,dS^T(1) ............................ P^T,dS^T(3) ...
+// (the tensor pipe executes one thread's MMAs in issue order, so S^T(st+2) may be issued over P^T(st) right behind
+// the products that read it).  Q and dO arrive as 64-row tiles in four 32 KB stages.
+//   tensor memory: S^T (2 x 64) | dP^T (2 x 64) | dV (128) | dK (128)
+//   shared memory: K, V (fixed) | [4 stages][Q 64 rows, dO 64 rows] | lse, delta of the step [group][parity][2][64]
+namespace dkdv {
+constexpr int kBQ = 64;                       // query rows per step
+constexpr int kStages = 4;
+constexpr int kQHalfBytes = kBQ * 128;        // one 64-column half of a 64-row tile
+constexpr int kQTileBytes = 2 * kQHalfBytes;  // 16 KB
+constexpr int kStageBytes = 2 * kQTileBytes;  // Q + dO
+constexpr int kSmemStream = 2 * kTileBytes;
+constexpr int kSmemVec = kSmemStream + kStages * kStageBytes;
+constexpr int kSmemBar = kSmemVec + 2 * 2 * 2 * kBQ * 4;
+constexpr int kNumBars = 14;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 32 + 1024;
+// S^T and dP^T of one step: M = 128 kv rows, N = 64 query rows
+constexpr uint32_t kIdescScores = (kIdescQK & ~(0x3fu << 17)) | ((kBQ >> 3) << 17);
+struct Bars {
+    uint32_t base;
+    __device__ uint32_t fixed_full() const { return base; }
+    __device__ uint32_t stream_full(int s) const { return base + 8 * (1 + s); }
+    __device__ uint32_t stream_empty(int s) const { return base + 8 * (5 + s); }
+    __device__ uint32_t s_full(int g) const { return base + 8 * (9 + g); }    // S^T, dP^T of group g's step landed
+    __device__ uint32_t ds_full(int g) const { return base + 8 * (11 + g); }  // P^T, dS^T of group g's step stored
+    __device__ uint32_t drain() const { return base + 8 * 13; }
+};
+}  // namespace dkdv
+
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+    using namespace dkdv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const Bars bars{base + kSmemBar};
-    float* vec = reinterpret_cast<float*>(gen_base + kSmemVec);  // [parity][0: lse*log2e, 1: delta*scale][128]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const dkdv::Bars bars{base + dkdv::kSmemBar};
+    float* vec = reinterpret_cast<float*>(gen_base + dkdv::kSmemVec);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + dkdv::kSmemBar + dkdv::kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + dkdv::kSmemBar + dkdv::kNumBars * 8 + 8);
+    // warp index through a shuffle: the compiler then knows it to be the same in every lane
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     long long id = blockIdx.x;
     const int split = static_cast<int>(id % p.head_splits);
@@ -478,19 +553,28 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int kvh = static_cast<int>(id % p.Hkv);
     const int b = static_cast<int>(id / p.Hkv);
     const int kv0 = jt * kBN;
-    const int i_lo = p.causal ? kv0 / kBM : 0;  // first query tile that can see this kv tile
-    int i_hi = p.n_qt;                          // one past the last one (a window ends it early)
+    const int i_lo = p.causal ? kv0 / kBQ : 0;  // first 64-row query tile that can see this kv tile
+    int i_hi = (p.Sq + kBQ - 1) / kBQ;          // one past the last one (a window ends it early)
     if (p.window > 0) {
-        const int lim = (kv0 + kBN - 1 + p.window - 1) / kBM + 1;
+        const int lim = (kv0 + kBN - 1 + p.window - 1) / kBQ + 1;
         i_hi = lim < i_hi ? lim : i_hi;
     }
-    const int n_i = i_hi - i_lo;                // may be <= 0 when Skv > Sq: nothing to accumulate
+    const int n_i = i_hi - i_lo;                 // may be <= 0 when Skv > Sq: nothing to accumulate
     const int heads_here = p.G / p.head_splits;  // head_splits divides G
     const int head0 = kvh * p.G + split * heads_here;
     const int n_steps = n_i > 0 ? n_i * heads_here : 0;
 
     if (threadIdx.x == 0) {
-        init_bars(bars);
+        mbar_init(bars.fixed_full(), 1);
+        for (int s = 0; s < dkdv::kStages; ++s) {
+            mbar_init(bars.stream_full(s), 1);
+            mbar_init(bars.stream_empty(s), 1);
+        }
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(bars.s_full(g), 1);
+            mbar_init(bars.ds_full(g), kBM);
+        }
+        mbar_init(bars.drain(), 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -504,8 +588,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
     const uint32_t sm_k = base, sm_v = base + kTileBytes;
-    auto sm_q = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes; };
-    auto sm_do = [&](int s) { return base + kSmemStream + s * 2 * kTileBytes + kTileBytes; };
+    auto sm_q = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes; };
+    auto sm_do = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes + kQTileBytes; };
 
     if (warp == 8) {
         if (lane == 0 && n_steps > 0) {
@@ -514,60 +598,133 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_load_4d(sm_k + kHalfBytes, &tm_k, bars.fixed_full(), 64, kv0, kvh, b);
             tma_load_4d(sm_v, &tm_v, bars.fixed_full(), 0, kv0, kvh, b);
             tma_load_4d(sm_v + kHalfBytes, &tm_v, bars.fixed_full(), 64, kv0, kvh, b);
+            int h = head0, i = 0;
             for (int st = 0; st < n_steps; ++st) {
-                const int s = st % kStages;
-                const uint32_t use = static_cast<uint32_t>(st / kStages);
-                const int h = head0 + st / n_i;
-                const int qrow0 = (i_lo + st % n_i) * kBM;
+                const int s = st % dkdv::kStages;
+                const uint32_t use = static_cast<uint32_t>(st / dkdv::kStages);
+                const int qrow0 = (i_lo + i) * kBQ;
                 mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, st);
-                mbar_arrive_expect_tx(bars.stream_full(s), 2 * kTileBytes);
+                mbar_arrive_expect_tx(bars.stream_full(s), kStageBytes);
                 tma_load_4d(sm_q(s), &tm_q, bars.stream_full(s), 0, qrow0, h, b);
-                tma_load_4d(sm_q(s) + kHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, h, b);
+                tma_load_4d(sm_q(s) + kQHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, h, b);
                 tma_load_4d(sm_do(s), &tm_do, bars.stream_full(s), 0, qrow0, h, b);
-                tma_load_4d(sm_do(s) + kHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, h, b);
+                tma_load_4d(sm_do(s) + kQHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, h, b);
+                if (++i == n_i) {
+                    i = 0;
+                    ++h;
+                }
             }
             if (*abort_flag) {
-                for (int st = (n_steps > kStages ? n_steps - kStages : 0); st < n_steps; ++st) {
+                for (int st = (n_steps > dkdv::kStages ? n_steps - dkdv::kStages : 0); st < n_steps; ++st) {
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(bars.stream_full(st % kStages), static_cast<uint32_t>(st / kStages) & 1u) &&
+                    while (!mbar_try_wait(bars.stream_full(st % dkdv::kStages),
+                                          static_cast<uint32_t>(st / dkdv::kStages) & 1u) &&
                            clock64() - t0 < kWaitLimitCycles / 64) {
                     }
                 }
             }
         }
     } else if (warp == 9) {
-        if (lane == 0 && n_steps > 0) {
+        // Lane 0 issues every MMA; the whole warp stays in the loop because the looks at the next step's barriers are
+        // taken by all lanes (one barrier per lane).  The issuing thread is the pace-maker of the block: a look at
+        // an mbarrier whose result is needed at once, or a commit, each leave the tensor pipe idle for the round trip
+        // (memory-pipe instructions are carried out in order behind the queued MMAs).  So a step is ONE run of 24
+        // MMAs -- dV, dK of step st, then S^T, dP^T of step st + 2 -- with the looks for the next run issued before
+        // the run's last four MMAs and read only after them, and both commits at the end of the run.
+        if (n_steps > 0) {
+            const uint32_t leader = lane == 0 ? 1u : 0u;
             mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
-            for (int st = 0; st < n_steps; ++st) {
-                const int s = st % kStages;
-                const uint32_t use = static_cast<uint32_t>(st / kStages);
-                mbar_wait(bars.stream_full(s), use & 1u, abort_flag, SITE_BWD_STREAM_FULL, st);
-                tc_fence_after();
+            // Low descriptor words (per k step and per stage only a constant is added: the tiles are 1024-byte aligned
+            // and no sum leaves the 14-bit address field).
+            const uint32_t hi = prefill::smem_desc_hi(1024);
+            const uint32_t k_lo = prefill::smem_desc_lo(sm_k, 16), v_lo = prefill::smem_desc_lo(sm_v, 16);
+            const uint32_t q_kmaj = prefill::smem_desc_lo(sm_q(0), 16), do_kmaj = prefill::smem_desc_lo(sm_do(0), 16);
+            const uint32_t q_mnmaj = prefill::smem_desc_lo(sm_q(0), kQHalfBytes);
+            const uint32_t do_mnmaj = prefill::smem_desc_lo(sm_do(0), kQHalfBytes);
+            constexpr uint32_t kOffKv4 = (kHalfBytes) >> 4, kOffQ4 = (kQHalfBytes) >> 4;  // k step 4: second 64-dim half
+            auto stream_parity = [&](int st) { return static_cast<uint32_t>(st / dkdv::kStages) & 1u; };
+            // S^T = K Q^T (all eight k steps) and the first four k steps of dP^T = V dO^T of step st
+            auto issue_scores_head = [&](int st) {
+                const uint32_t soff = static_cast<uint32_t>(st % dkdv::kStages) * (kStageBytes >> 4);
+                const uint32_t col = static_cast<uint32_t>(st & 1) * kBQ;
+                const uint32_t qa = q_kmaj + soff, da = do_kmaj + soff;
+                tc_mma_ss_lo_if<false>(leader, tm_st + col, k_lo, qa, hi, kIdescScores);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // S^T = K Q^T
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tm_st, smem_desc(sm_k + off, 16, 1024), smem_desc(sm_q(s) + off, 16, 1024), kIdescQK,
-                              ks > 0 ? 1u : 0u);
+                for (int ks = 1; ks < 8; ++ks)
+                    tc_mma_ss_lo_if<true>(leader, tm_st + col, k_lo + (((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4),
+                                          qa + (((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4), hi, kIdescScores);
+                tc_mma_ss_lo_if<false>(leader, tm_dpt + col, v_lo, da, hi, kIdescScores);
+#pragma unroll
+                for (int ks = 1; ks < 4; ++ks)
+                    tc_mma_ss_lo_if<true>(leader, tm_dpt + col, v_lo + ((ks * 32) >> 4), da + ((ks * 32) >> 4), hi,
+                                          kIdescScores);
+            };
+            // the last four k steps of dP^T of step st, with a look at (bar, par) issued first and read afterwards
+            auto issue_scores_tail = [&](int st, uint32_t bar, uint32_t par) {
+                const uint32_t soff = static_cast<uint32_t>(st % dkdv::kStages) * (kStageBytes >> 4);
+                const uint32_t col = static_cast<uint32_t>(st & 1) * kBQ;
+                return tc_ss4_run_after_look(tm_dpt + col, v_lo + kOffKv4, do_kmaj + soff + kOffQ4, hi, kIdescScores,
+                                             leader, bar, par);
+            };
+            // what a lane looks at before the run of step st: lane 0 ds_full(st), lane 1 stream_full(st + 2) (the
+            // other lanes, and lane 1 when there is no step st + 2, repeat lane 0)
+            auto my_barrier = [&](int st, uint32_t& bar, uint32_t& par, int& site) {
+                bar = bars.ds_full(st & 1);
+                par = static_cast<uint32_t>(st >> 1) & 1u;
+                site = SITE_BWD_DS_FULL;
+                if (lane == 1 && st + 2 < n_steps) {
+                    bar = bars.stream_full((st + 2) % dkdv::kStages);
+                    par = stream_parity(st + 2);
+                    site = SITE_BWD_STREAM_FULL;
                 }
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // dP^T = V dO^T
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tm_dpt, smem_desc(sm_v + off, 16, 1024), smem_desc(sm_do(s) + off, 16, 1024), kIdescQK,
-                              ks > 0 ? 1u : 0u);
-                }
-                tc_commit(bars.s_full());
-                mbar_wait(bars.ds_full(), static_cast<uint32_t>(st) & 1u, abort_flag, SITE_BWD_DS_FULL, st);
+            };
+            for (int st = 0; st < 2 && st < n_steps; ++st) {
+                mbar_wait(bars.stream_full(st), 0, abort_flag, SITE_BWD_STREAM_FULL, st);
                 tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)  // dV += P^T dO
-                    tc_mma_ts(tm_dv, tm_st + a_col(ks), smem_desc(sm_do(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
-                              (st == 0 && ks == 0) ? 0u : 1u);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)  // dK += dS^T Q
-                    tc_mma_ts(tm_dk, tm_dpt + a_col(ks), smem_desc(sm_q(s) + ks * 2048, kHalfBytes, 1024), kIdescPV,
-                              (st == 0 && ks == 0) ? 0u : 1u);
-                tc_commit(bars.stream_empty(s));
+                issue_scores_head(st);
+                issue_scores_tail(st, bars.stream_full(st), 0);
+                tc_commit_if(leader, bars.s_full(st & 1));
             }
+            bool seen = false;
+#pragma unroll 1
+            for (int st = 0; st < n_steps; ++st) {
+                uint32_t my_bar, my_par;
+                int my_site;
+                if (!seen) {
+                    my_barrier(st, my_bar, my_par, my_site);
+                    if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                        if (lane < 2) mbar_wait(my_bar, my_par, abort_flag, my_site, st);
+                        __syncwarp();
+                    }
+                }
+                const bool more = st + 2 < n_steps;
+                const uint32_t soff = static_cast<uint32_t>(st % dkdv::kStages) * (kStageBytes >> 4);
+                const uint32_t col = static_cast<uint32_t>(st & 1) * kBQ;
+                const uint32_t db = do_mnmaj + soff, qb = q_mnmaj + soff;
+                const uint32_t acc0 = st == 0 ? 0u : 1u;
+                tc_fence_after();
+                tc_mma_ts_lo_if(leader, tm_dv, tm_st + col, db, hi, kIdescPV, acc0);  // dV (+)= P^T dO
+#pragma unroll
+                for (int ks = 1; ks < 4; ++ks)
+                    tc_mma_ts_lo_if(leader, tm_dv, tm_st + col + ks * 8, db + ks * (2048 >> 4), hi, kIdescPV, 1u);
+                tc_mma_ts_lo_if(leader, tm_dk, tm_dpt + col, qb, hi, kIdescPV, acc0);  // dK (+)= dS^T Q
+#pragma unroll
+                for (int ks = 1; ks < 4; ++ks)
+                    tc_mma_ts_lo_if(leader, tm_dk, tm_dpt + col + ks * 8, qb + ks * (2048 >> 4), hi, kIdescPV, 1u);
+                if (more) issue_scores_head(st + 2);
+                seen = false;
+                if (st + 1 < n_steps) {
+                    my_barrier(st + 1, my_bar, my_par, my_site);
+                    const uint32_t mine =
+                        more ? issue_scores_tail(st + 2, my_bar, my_par) : (mbar_try_wait(my_bar, my_par) ? 1u : 0u);
+                    seen = __all_sync(0xffffffffu, mine != 0);
+                }
+                if (more) tc_commit_if(leader, bars.s_full(st & 1));
+                tc_commit_if(leader, bars.stream_empty(st % dkdv::kStages));
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && n_steps > 0) {
             tc_commit(bars.drain());
             mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 0);
             if (*abort_flag) {
@@ -577,29 +734,34 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
         }
     } else {
-        // element-wise: thread = (kv row, 64 of the 128 query columns of the current query tile)
-        const int half = warp >> 2;
+        // element-wise: thread = (kv row, group); a group takes every other step (64 query columns)
+        const int grp = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const int kvi = kv0 + row;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t my_st = tm_st + lane_base + grp * kBQ, my_dpt = tm_dpt + lane_base + grp * kBQ;
         const float c = p.scale * kLog2e;
-        const int tid = threadIdx.x;  // 0..255 here
+        const int gtid = threadIdx.x & 127;
+        float* vgrp = vec + grp * (2 * 2 * kBQ);
+        int h = head0, i = grp;
+        while (n_i > 0 && i >= n_i) {
+            i -= n_i;
+            ++h;
+        }
 #pragma unroll 1
-        for (int st = 0; st < n_steps; ++st) {
-            const int h = head0 + st / n_i;
-            const int qrow0 = (i_lo + st % n_i) * kBM;
-            // stage lse*log2e and delta of the 128 query rows of this step (zeros beyond Sq)
-            float* vbuf = vec + (st & 1) * 256;
+        for (int st = grp, it = 0; st < n_steps; st += 2, ++it) {
+            const int qrow0 = (i_lo + i) * kBQ;
+            // stage lse*log2e and delta*scale of the 64 query rows of this step (zeros beyond Sq)
+            float* vbuf = vgrp + (it & 1) * (2 * kBQ);
             {
-                const int r = tid & 127;
-                const int qr = qrow0 + r;
+                const int qr = qrow0 + (gtid & (kBQ - 1));
                 const long long vi = (static_cast<long long>(b) * p.Hq + h) * p.Sq + qr;
                 float val = 0.f;
-                if (qr < p.Sq) val = tid < 128 ? p.lse[vi] * kLog2e : p.delta[vi] * p.scale;
-                vbuf[tid] = val;
+                if (qr < p.Sq) val = gtid < kBQ ? p.lse[vi] * kLog2e : p.delta[vi] * p.scale;
+                vbuf[gtid] = val;
             }
-            named_bar_sync(1, 2 * kBM);
-            mbar_wait(bars.s_full(), static_cast<uint32_t>(st) & 1u, abort_flag, SITE_BWD_S_FULL, st);
+            named_bar_sync(1 + grp, kBM);
+            mbar_wait(bars.s_full(grp), static_cast<uint32_t>(it) & 1u, abort_flag, SITE_BWD_S_FULL, st);
             __syncwarp();
             tc_fence_after();
             // query columns that see this kv row: q >= kv (causal) and q < Sq (only edge tiles need the test)
@@ -609,21 +771,21 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const int wl = kvi + (p.window - 1) - qrow0;  // last query that still has this kv in its window
                 limit = wl < limit ? wl : limit;
             }
-            const bool need_mask = (qrow0 + kBM > p.Sq) || (p.causal && (kv0 + kBN - 1 > qrow0)) ||
-                                   (p.window > 0 && (qrow0 + kBM - 1 > kv0 + (p.window - 1)));
+            const bool need_mask = (qrow0 + kBQ > p.Sq) || (p.causal && (kv0 + kBN - 1 > qrow0)) ||
+                                   (p.window > 0 && (qrow0 + kBQ - 1 > kv0 + (p.window - 1)));
             const uint64_t c2 = pk2(c, c), sc2 = pk2(p.scale, p.scale);
             uint32_t pkp[32], pkd[32];
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
-                const int col0 = half * 64 + cc * 32;
+                const int col0 = cc * 32;
                 float sv[32], dpv[32];
-                tmem_ld32_wait(tm_st + lane_base + col0, sv);
-                tmem_ld32_wait(tm_dpt + lane_base + col0, dpv);
+                tmem_ld32_wait(my_st + col0, sv);
+                tmem_ld32_wait(my_dpt + col0, dpv);
 #pragma unroll
                 for (int e = 0; e < 32; e += 4) {
                     // lse*log2e and delta*scale of four query columns at a time (same address for the whole warp)
                     const float4 l4 = *reinterpret_cast<const float4*>(vbuf + col0 + e);
-                    const float4 d4 = *reinterpret_cast<const float4*>(vbuf + 128 + col0 + e);
+                    const float4 d4 = *reinterpret_cast<const float4*>(vbuf + kBQ + col0 + e);
 #pragma unroll
                     for (int u = 0; u < 4; u += 2) {
                         const int q_a = col0 + e + u, q_b = q_a + 1;
@@ -643,13 +805,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     }
                 }
             }
-            tmem_st32(tm_st + lane_base + half * 64, pkp);
-            tmem_st32(tm_dpt + lane_base + half * 64, pkd);
+            tmem_st32(my_st, pkp);
+            tmem_st32(my_dpt, pkd);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bars.ds_full());
+            mbar_arrive(bars.ds_full(grp));
+            i += 2;
+            while (i >= n_i) {
+                i -= n_i;
+                ++h;
+            }
         }
-        // epilogue: dV, dK -> bf16 (zeros when no query tile reaches this kv tile)
+        // epilogue: dV, dK -> bf16 (zeros when no query tile reaches this kv tile); thread = (kv row, 64 of 128 dims)
+        const int half = grp;
         if (n_steps > 0) {
             mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 1);
             __syncwarp();
@@ -798,15 +966,18 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
         (p.head_splits > 1 && blocks_reduce > 0x7fffffffLL))
         return CLLO_E_UNSUPPORTED;
 
-    CUtensorMap tm_q, tm_k, tm_v, tm_do;
+    CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_q64, tm_do64;  // the dK/dV kernel takes Q and dO in 64-row tiles
     if ((rc = prefill::encode_bhsd_map(&tm_q, q, B, Hq, Sq)) != CLLO_OK) return rc;
     if ((rc = prefill::encode_bhsd_map(&tm_k, k, B, Hkv, Skv)) != CLLO_OK) return rc;
     if ((rc = prefill::encode_bhsd_map(&tm_v, v, B, Hkv, Skv)) != CLLO_OK) return rc;
     if ((rc = prefill::encode_bhsd_map(&tm_do, grad_o, B, Hq, Sq)) != CLLO_OK) return rc;
+    if ((rc = prefill::encode_bhsd_map(&tm_q64, q, B, Hq, Sq, dkdv::kBQ)) != CLLO_OK) return rc;
+    if ((rc = prefill::encode_bhsd_map(&tm_do64, grad_o, B, Hq, Sq, dkdv::kBQ)) != CLLO_OK) return rc;
 
     if (!di->backward_attr_set) {
         CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::kSmemBytes));
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        CLLO_CUDA_TRY(
+            cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkdv::kSmemBytes));
         di->backward_attr_set = true;
     }
     bwd_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
@@ -815,7 +986,7 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     CLLO_CUDA_TRY(cudaGetLastError());
     bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, dq::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
-    bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
+    bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, dkdv::kSmemBytes, stream>>>(tm_q64, tm_k, tm_v, tm_do64, p);
     CLLO_CUDA_TRY(cudaGetLastError());
     if (p.head_splits > 1) {
         bwd_reduce_kernel<<<static_cast<unsigned>(blocks_reduce), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,

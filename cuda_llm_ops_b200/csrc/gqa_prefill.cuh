@@ -847,12 +847,12 @@ prefill_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, int S) {
+static int encode_bhsd_map(CUtensorMap* map, const void* basep, int B, int H, int S, uint32_t box_rows = 128) {
     const uint64_t row = static_cast<uint64_t>(kD) * 2;
     const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(S), static_cast<uint64_t>(H),
                               static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {row, row * S, row * S * H};
-    const uint32_t box[4] = {64, 128, 1, 1};
+    const uint32_t box[4] = {64, box_rows, 1, 1};
     return encode_bf16_4d(map, basep, dims, strides, box);
 }
 
