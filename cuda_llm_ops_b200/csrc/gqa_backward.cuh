@@ -43,6 +43,9 @@ using prefill::tc_fence_after;
 using prefill::tc_fence_before;
 using prefill::tc_mma_ss;
 using prefill::tc_mma_ts;
+using prefill::tc_commit_if;
+using prefill::tc_mma_ss_lo_if;
+using prefill::tc_mma_ts_lo_if;
 using prefill::tmem_alloc;
 using prefill::tmem_dealloc;
 using prefill::tmem_ld32_wait;
@@ -150,7 +153,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const dq::Bars bars{base + dq::kSmemBar};
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + dq::kSmemBar + dq::kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + dq::kSmemBar + dq::kNumBars * 8 + 8);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp index through a shuffle: the compiler then knows it to be the same in every lane
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     long long id = blockIdx.x;
     const int g = static_cast<int>(id % p.G);
@@ -248,30 +252,35 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     } else if (warp == 9) {
         // One thread issues every MMA; per kv tile one run of 16 (S and dP of the NEXT tile) and one of 8 (dQ of this
         // tile), each behind one look at its barriers (the whole warp looks at once, one barrier per lane).
+        // The whole warp runs the issue code with the MMAs predicated on the leader lane (see tc_mma_ss_lo_if), on the
+        // low words of the descriptors (per k step and per stage only a constant is added).
+        const uint32_t leader = lane == 0 ? 1u : 0u;
+        const uint32_t hi = prefill::smem_desc_hi(1024);
+        const uint32_t q_lo = prefill::smem_desc_lo(sm_q, 16), do_lo = prefill::smem_desc_lo(sm_do, 16);
+        const uint32_t k_kmaj = prefill::smem_desc_lo(sm_k(0), 16), v_kmaj = prefill::smem_desc_lo(sm_v(0), 16);
+        const uint32_t k_mnmaj = prefill::smem_desc_lo(sm_k(0), kHalfBytes);
         auto issue_sdp = [&](int j) {
-            const uint32_t ka = sm_k(j % dq::kKStages), va = sm_v(j & 1);
+            const uint32_t ka = k_kmaj + static_cast<uint32_t>(j % dq::kKStages) * (kTileBytes >> 4);
+            const uint32_t va = v_kmaj + static_cast<uint32_t>(j & 1) * (kTileBytes >> 4);
+            tc_mma_ss_lo_if<false>(leader, tm_s, q_lo, ka, hi, kIdescQK);  // S = Q K^T
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {  // S = Q K^T
-                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                tc_mma_ss(tm_s, smem_desc(sm_q + off, 16, 1024), smem_desc(ka + off, 16, 1024), kIdescQK,
-                          ks > 0 ? 1u : 0u);
+            for (int ks = 1; ks < 8; ++ks) {
+                const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                tc_mma_ss_lo_if<true>(leader, tm_s, q_lo + off, ka + off, hi, kIdescQK);
             }
+            tc_mma_ss_lo_if<false>(leader, tm_dp, do_lo, va, hi, kIdescQK);  // dP = dO V^T
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {  // dP = dO V^T
-                const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                tc_mma_ss(tm_dp, smem_desc(sm_do + off, 16, 1024), smem_desc(va + off, 16, 1024), kIdescQK,
-                          ks > 0 ? 1u : 0u);
+            for (int ks = 1; ks < 8; ++ks) {
+                const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                tc_mma_ss_lo_if<true>(leader, tm_dp, do_lo + off, va + off, hi, kIdescQK);
             }
         };
-        if (lane == 0) {
-            mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
-            mbar_wait(bars.k_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
-            mbar_wait(bars.v_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
-            tc_fence_after();
-            issue_sdp(0);
-            tc_commit(bars.sdp_full(0));
-        }
-        __syncwarp();
+        mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
+        mbar_wait(bars.k_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
+        mbar_wait(bars.v_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
+        tc_fence_after();
+        issue_sdp(0);
+        tc_commit_if(leader, bars.sdp_full(0));
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
             if (j + 1 < n_kv) {
@@ -288,27 +297,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if (lane < 3) mbar_wait(my_bar, my_par, abort_flag, SITE_BWD_STREAM_FULL, j);
                     __syncwarp();
                 }
-                if (lane == 0) {
-                    tc_fence_after();
-                    issue_sdp(j + 1);
-                    tc_commit(bars.sdp_full((j + 1) & 1));
-                }
-                __syncwarp();
-            }
-            if (lane == 0) {
-                mbar_wait(bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
                 tc_fence_after();
-                const uint32_t ka = sm_k(j % dq::kKStages);
-                const uint32_t dsa = tmem_base + dq::kColDS + (j & 1) * 64;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)  // dQ += dS K   (K tile as the MN-major B operand)
-                    tc_mma_ts(tm_dq, dsa + ks * 8, smem_desc(ka + ks * 2048, kHalfBytes, 1024), kIdescPV,
-                              (j == 0 && ks == 0) ? 0u : 1u);
-                tc_commit(bars.dq_done(j & 1));
-                tc_commit(bars.k_empty(j % dq::kKStages));
+                issue_sdp(j + 1);
+                tc_commit_if(leader, bars.sdp_full((j + 1) & 1));
             }
-            __syncwarp();
+            mbar_wait(bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
+            tc_fence_after();
+            const uint32_t kb = k_mnmaj + static_cast<uint32_t>(j % dq::kKStages) * (kTileBytes >> 4);
+            const uint32_t dsa = tmem_base + dq::kColDS + (j & 1) * 64;
+            tc_mma_ts_lo_if(leader, tm_dq, dsa, kb, hi, kIdescPV, j == 0 ? 0u : 1u);  // dQ (+)= dS K (K MN-major)
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks)
+                tc_mma_ts_lo_if(leader, tm_dq, dsa + ks * 8, kb + ks * (2048 >> 4), hi, kIdescPV, 1u);
+            tc_commit_if(leader, bars.dq_done(j & 1));
+            tc_commit_if(leader, bars.k_empty(j % dq::kKStages));
         }
+        __syncwarp();
         if (lane == 0) {
             tc_commit(bars.drain());
             mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 0);
@@ -423,44 +427,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-}
-
-// tcgen05.mma / commit issued by the lanes whose `leader` is non-zero while the WHOLE warp runs the surrounding code:
-// the operands (descriptor words, tensor-memory addresses) are then warp-uniform values that the compiler keeps in
-// uniform registers.  Under an `if (lane == 0)` they live in ordinary registers and every MMA pays several
-// register-to-uniform moves in the issuing thread -- measured here: 75-95 cycles per MMA issued, against 48-64 that
-// the tensor pipe needs.
-template <bool kAccumulate>
-__device__ __forceinline__ void tc_mma_ss_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
-                                                uint32_t hi, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 q, %6, 0;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 da, {%1, %3};\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0), "r"(leader)
-        : "memory");
-}
-__device__ __forceinline__ void tc_mma_ts_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                                uint32_t hi, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
-        "setp.ne.b32 q, %6, 0;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(leader)
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint32_t bar) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-        ::"r"(bar), "r"(leader)
-        : "memory");
 }
 
 // Four S-type MMAs (both operands in shared memory, k steps 32 bytes apart, all accumulating) issued by the leader

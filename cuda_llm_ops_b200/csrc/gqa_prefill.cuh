@@ -155,6 +155,44 @@ __device__ __forceinline__ void tc_mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
+// tcgen05.mma / commit issued by the lanes whose `leader` is non-zero while the WHOLE warp runs the surrounding code:
+// the operands (descriptor words, tensor-memory addresses) are then warp-uniform values that the compiler keeps in
+// uniform registers.  Under an `if (lane == 0)` they live in ordinary registers and every MMA pays several
+// register-to-uniform moves in the issuing thread -- measured here: 75-95 cycles per MMA issued, against 48-64 that
+// the tensor pipe needs.
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ss_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                uint32_t hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_lo_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                uint32_t hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(leader)
+        : "memory");
+}
+
 // O += P V (eight MMAs, A from tensor memory) by the leader lane, with a look at an mbarrier (one barrier per
 // lane) put between the fifth and the sixth MMA and its result read only after the eighth.  Memory-pipe
 // instructions of a warp are carried out in order, so a look whose result is needed at once keeps the thread from
