@@ -110,7 +110,8 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t bar_drain = bar0 + 8 * 13;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemBar + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemBar + kNumBars * 8 + 8);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp index through a shuffle: the compiler then knows it to be the same in every lane
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     // block -> (batch, kv head, query tile, head in group); heads of one group are neighbours so that they stream
     // the same K/V tiles through L2 together; heavy (late) causal tiles go first
@@ -231,16 +232,27 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tc_mma_ss_lo<true>(c, q_lo + off, ka + off, hi, kIdescQK);
             }
         };
-        auto issue_pv = [&](int j) {  // O += P[j % 2] V(j)
+        // In the main loop the whole warp runs the issue code and the leader lane's predicate guards the MMAs, so
+        // that the operands are warp-uniform values (see tc_mma_ss_lo_if).
+        const uint32_t leader = lane == 0 ? 1u : 0u;
+        auto issue_s_all = [&](int j) {  // S(j) -> C[j % 2]
+            const uint32_t ka = (j & 1) ? k_lo1 : k_lo0;
+            const uint32_t c = tmem_base + kColC + (j & 1) * kBN;
+            prefill::tc_mma_ss_lo_if<false>(leader, c, q_lo, ka, hi, kIdescQK);
+#pragma unroll
+            for (int ks = 1; ks < kDqk / 16; ++ks) {
+                const uint32_t off = ((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4;
+                prefill::tc_mma_ss_lo_if<true>(leader, c, q_lo + off, ka + off, hi, kIdescQK);
+            }
+        };
+        auto issue_pv_all = [&](int j) {  // O += P[j % 2] V(j)
             const uint32_t va = (j & 1) ? v_lo1 : v_lo0;
             const uint32_t pa = tmem_base + kColP + (j & 1) * 64;
             const uint32_t oa = tmem_base + kColO;
-            if (j == 0)
-                tc_mma_ts_lo<false>(oa, pa, va, hi, kIdescPV);
-            else
-                tc_mma_ts_lo<true>(oa, pa, va, hi, kIdescPV);
+            prefill::tc_mma_ts_lo_if(leader, oa, pa, va, hi, kIdescPV, j == 0 ? 0u : 1u);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc_mma_ts_lo<true>(oa, pa + ks * 8, va + ks * (2048 >> 4), hi, kIdescPV);
+            for (int ks = 1; ks < 8; ++ks)
+                prefill::tc_mma_ts_lo_if(leader, oa, pa + ks * 8, va + ks * (2048 >> 4), hi, kIdescPV, 1u);
         };
         if (lane == 0) {
             mbar_wait(bar_q_full, 0, abort_flag, SITE_MLA_Q, 0);
@@ -275,17 +287,15 @@ mla_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (lane < 4) mbar_wait(my_bar, my_par, abort_flag, my_site, j);
                 __syncwarp();
             }
-            if (lane == 0) {
-                tc_fence_after();
-                issue_pv(j);
-                tc_commit(bar_pv_done(s));
-                if (more) {
-                    issue_s(j + 2);
-                    tc_commit(bar_s_full(s));
-                }
+            tc_fence_after();
+            issue_pv_all(j);
+            prefill::tc_commit_if(leader, bar_pv_done(s));
+            if (more) {
+                issue_s_all(j + 2);
+                prefill::tc_commit_if(leader, bar_s_full(s));
             }
-            __syncwarp();
         }
+        __syncwarp();
         if (lane == 0) {
             // everything issued must have retired before tensor memory is released
             tc_commit(bar_drain);
