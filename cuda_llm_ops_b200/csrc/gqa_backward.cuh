@@ -113,6 +113,37 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
     if (lane == 0) delta[row] = acc;
 }
 
+// Four S-type MMAs (both operands in shared memory, k steps 32 bytes apart, all accumulating) issued by the leader
+// lane, behind a look at an mbarrier that every lane takes at its own barrier and reads only after the fourth MMA,
+// so that the round trip of the look is covered by the MMAs.
+__device__ __forceinline__ uint32_t tc_ss4_run_after_look(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                          uint32_t idesc, uint32_t leader, uint32_t look_bar,
+                                                          uint32_t look_parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pt, q, w;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 a, b;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 w, [%7], %8;\n\t"
+        "mov.b64 da, {%2, %4};\n\t mov.b64 db, {%3, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 2;\n\t add.u32 b, %3, 2;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 4;\n\t add.u32 b, %3, 4;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "add.u32 a, %2, 6;\n\t add.u32 b, %3, 6;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
+        "selp.u32 %0, 1, 0, w;\n\t"
+        "}"
+        : "=r"(seen)
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(leader), "r"(look_bar), "r"(look_parity)
+        : "memory");
+    return seen;
+}
+
 // ------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------
@@ -259,56 +290,78 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t q_lo = prefill::smem_desc_lo(sm_q, 16), do_lo = prefill::smem_desc_lo(sm_do, 16);
         const uint32_t k_kmaj = prefill::smem_desc_lo(sm_k(0), 16), v_kmaj = prefill::smem_desc_lo(sm_v(0), 16);
         const uint32_t k_mnmaj = prefill::smem_desc_lo(sm_k(0), kHalfBytes);
-        auto issue_sdp = [&](int j) {
+        // S = Q K^T and dP = dO V^T of tile j; the last four k steps of dP go out behind a look at (bar, par) that
+        // every lane takes and reads after them
+        auto issue_sdp = [&](int j, uint32_t bar, uint32_t par) {
             const uint32_t ka = k_kmaj + static_cast<uint32_t>(j % dq::kKStages) * (kTileBytes >> 4);
             const uint32_t va = v_kmaj + static_cast<uint32_t>(j & 1) * (kTileBytes >> 4);
-            tc_mma_ss_lo_if<false>(leader, tm_s, q_lo, ka, hi, kIdescQK);  // S = Q K^T
+            tc_mma_ss_lo_if<false>(leader, tm_s, q_lo, ka, hi, kIdescQK);
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks) {
                 const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
                 tc_mma_ss_lo_if<true>(leader, tm_s, q_lo + off, ka + off, hi, kIdescQK);
             }
-            tc_mma_ss_lo_if<false>(leader, tm_dp, do_lo, va, hi, kIdescQK);  // dP = dO V^T
+            tc_mma_ss_lo_if<false>(leader, tm_dp, do_lo, va, hi, kIdescQK);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) {
-                const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-                tc_mma_ss_lo_if<true>(leader, tm_dp, do_lo + off, va + off, hi, kIdescQK);
+            for (int ks = 1; ks < 4; ++ks)
+                tc_mma_ss_lo_if<true>(leader, tm_dp, do_lo + ((ks * 32) >> 4), va + ((ks * 32) >> 4), hi, kIdescQK);
+            return tc_ss4_run_after_look(tm_dp, do_lo + (kHalfBytes >> 4), va + (kHalfBytes >> 4), hi, kIdescQK, leader,
+                                         bar, par);
+        };
+        // what a lane looks at before S, dP of tile j + 1 are issued: lane 0 S, dP of tile j copied out; 1 K(j + 1)
+        // arrived; 2 V(j + 1) arrived (the other lanes repeat lane 0)
+        auto landing_barrier = [&](int j, uint32_t& bar, uint32_t& par) {
+            bar = bars.c_free();
+            par = static_cast<uint32_t>(j) & 1u;
+            if (lane == 1) {
+                bar = bars.k_full((j + 1) % dq::kKStages);
+                par = static_cast<uint32_t>((j + 1) / 3) & 1u;
+            } else if (lane == 2) {
+                bar = bars.v_full((j + 1) & 1);
+                par = static_cast<uint32_t>((j + 1) >> 1) & 1u;
             }
         };
         mbar_wait(bars.fixed_full(), 0, abort_flag, SITE_BWD_FIXED, 0);
         mbar_wait(bars.k_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
         mbar_wait(bars.v_full(0), 0, abort_flag, SITE_BWD_STREAM_FULL, 0);
         tc_fence_after();
-        issue_sdp(0);
+        issue_sdp(0, bars.fixed_full(), 0);
         tc_commit_if(leader, bars.sdp_full(0));
+        // Per kv tile two runs, S, dP of the next tile (16 MMAs) and dQ of this tile (8); each run carries, before its
+        // last MMAs, the look at the barriers of the run after it, read when the run has been issued.
+        bool landing_seen = false;
 #pragma unroll 1
         for (int j = 0; j < n_kv; ++j) {
+            uint32_t my_bar, my_par;
+            bool ds_seen = false;
             if (j + 1 < n_kv) {
-                // lane 0: S, dP of tile j copied out; 1: K(j+1) arrived; 2: V(j+1) arrived
-                uint32_t my_bar = bars.c_free(), my_par = static_cast<uint32_t>(j) & 1u;
-                if (lane == 1) {
-                    my_bar = bars.k_full((j + 1) % dq::kKStages);
-                    my_par = static_cast<uint32_t>((j + 1) / 3) & 1u;
-                } else if (lane == 2) {
-                    my_bar = bars.v_full((j + 1) & 1);
-                    my_par = static_cast<uint32_t>((j + 1) >> 1) & 1u;
-                }
-                if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
-                    if (lane < 3) mbar_wait(my_bar, my_par, abort_flag, SITE_BWD_STREAM_FULL, j);
-                    __syncwarp();
+                if (!landing_seen) {
+                    landing_barrier(j, my_bar, my_par);
+                    if (!__all_sync(0xffffffffu, mbar_try_wait(my_bar, my_par))) {
+                        if (lane < 3) mbar_wait(my_bar, my_par, abort_flag, SITE_BWD_STREAM_FULL, j);
+                        __syncwarp();
+                    }
                 }
                 tc_fence_after();
-                issue_sdp(j + 1);
+                const uint32_t mine = issue_sdp(j + 1, bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u);
                 tc_commit_if(leader, bars.sdp_full((j + 1) & 1));
+                ds_seen = __all_sync(0xffffffffu, mine != 0);
             }
-            mbar_wait(bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
+            if (!ds_seen)
+                mbar_wait(bars.ds_full(j & 1), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, SITE_BWD_DS_FULL, j);
             tc_fence_after();
             const uint32_t kb = k_mnmaj + static_cast<uint32_t>(j % dq::kKStages) * (kTileBytes >> 4);
             const uint32_t dsa = tmem_base + dq::kColDS + (j & 1) * 64;
-            tc_mma_ts_lo_if(leader, tm_dq, dsa, kb, hi, kIdescPV, j == 0 ? 0u : 1u);  // dQ (+)= dS K (K MN-major)
-#pragma unroll
-            for (int ks = 1; ks < 8; ++ks)
-                tc_mma_ts_lo_if(leader, tm_dq, dsa + ks * 8, kb + ks * (2048 >> 4), hi, kIdescPV, 1u);
+            // dQ (+)= dS K (K tile as the MN-major B operand), with the look for S, dP of tile j + 2
+            if (j + 2 < n_kv) {
+                landing_barrier(j + 1, my_bar, my_par);
+            } else {
+                my_bar = bars.fixed_full();
+                my_par = 0;
+            }
+            const uint32_t mine = prefill::tc_pv_run_with_look(tm_dq, dsa, kb, hi, kIdescPV, j == 0 ? 0u : 1u, leader,
+                                                               my_bar, my_par);
+            landing_seen = __all_sync(0xffffffffu, mine != 0);
             tc_commit_if(leader, bars.dq_done(j & 1));
             tc_commit_if(leader, bars.k_empty(j % dq::kKStages));
         }
@@ -427,37 +480,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-}
-
-// Four S-type MMAs (both operands in shared memory, k steps 32 bytes apart, all accumulating) issued by the leader
-// lane, behind a look at an mbarrier that every lane takes at its own barrier and reads only after the fourth MMA,
-// so that the round trip of the look is covered by the MMAs.
-__device__ __forceinline__ uint32_t tc_ss4_run_after_look(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
-                                                          uint32_t idesc, uint32_t leader, uint32_t look_bar,
-                                                          uint32_t look_parity) {
-    uint32_t seen;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred pt, q, w;\n\t"
-        ".reg .b64 da, db;\n\t"
-        ".reg .b32 a, b;\n\t"
-        "setp.ne.b32 q, %6, 0;\n\t"
-        "setp.eq.b32 pt, 0, 0;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 w, [%7], %8;\n\t"
-        "mov.b64 da, {%2, %4};\n\t mov.b64 db, {%3, %4};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
-        "add.u32 a, %2, 2;\n\t add.u32 b, %3, 2;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
-        "add.u32 a, %2, 4;\n\t add.u32 b, %3, 4;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
-        "add.u32 a, %2, 6;\n\t add.u32 b, %3, 6;\n\t mov.b64 da, {a, %4};\n\t mov.b64 db, {b, %4};\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %5, pt;\n\t"
-        "selp.u32 %0, 1, 0, w;\n\t"
-        "}"
-        : "=r"(seen)
-        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(leader), "r"(look_bar), "r"(look_parity)
-        : "memory");
-    return seen;
 }
 
 // ------------------------------------------------------------------------------------------------
