@@ -5,19 +5,23 @@
 //                     dS = P o (dP - D) * scale with P = exp(scale*S - lse) (no row reduction: the forward
 //                     pass left lse, a small pre-pass leaves D = rowsum(dO o O)); dS goes back to tensor
 //                     memory as bf16 (a region of its own, two buffers) and feeds dQ += dS K as the A operand.
-//   bwd_dkdv_kernel   one block per (batch, kv head, 128 kv rows); loops over all query tiles of all heads
-//                     of the group.  It forms the TRANSPOSED tiles directly, S^T = K Q^T and
+//   bwd_dkdv_kernel   one block per (batch, kv head, 128 kv rows); loops over all query rows of all heads of
+//                     the group in steps of 64 rows.  It forms the TRANSPOSED tiles directly, S^T = K Q^T and
 //                     dP^T = V dO^T, so that P^T and dS^T are again A operands in tensor memory for
 //                     dV += P^T dO and dK += dS^T Q: no transposes through shared memory, and dK/dV are
 //                     summed over the heads of the group in the accumulators: one rounding, deterministic.
+//                     Steps alternate between two element-wise groups with their own halves of S^T and dP^T,
+//                     so the products of one step run while the other step's P^T, dS^T are being formed.
 //                     When (kv head, kv tile) pairs are too few to fill the GPU (one kv head, short
 //                     sequence) the heads of a group are divided among several blocks; their fp32 partials
 //                     go to the workspace and bwd_reduce_kernel sums them in a fixed order.
 //
 // Both recompute S and dP (7 tile products per (q tile, kv tile) instead of the minimal 5); in exchange no
-// gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dS[0] | dS[1] | dQ (pipelined over the
-// kv tiles, see there), dK/dV kernel S^T | dP^T | dV | dK (all 512, P^T and dS^T written over S^T and dP^T).  Shared-memory operand layouts, descriptors, TMA boxes and
-// barrier conventions are those of the forward kernel (gqa_prefill.cuh).
+// gradient is accumulated through global memory.  Tensor memory: dQ kernel S | dP | dS[0] | dS[1] | dQ (pipelined
+// over the kv tiles, see there), dK/dV kernel S^T (2 x 64) | dP^T (2 x 64) | dV | dK (all 512 columns; P^T and dS^T
+// are written over S^T and dP^T).  Shared-memory operand layouts, descriptors, TMA boxes and barrier conventions
+// are those of the forward kernel (gqa_prefill.cuh).  In both kernels the warp that issues the MMAs runs its loop
+// as a whole warp with the MMAs predicated on one lane (tc_mma_ss_lo_if): it is the pace-maker of the block.
 //
 // Upstream: flash_gqa_backward_bf16_kernel, src/python/Triton/flash_gqa_backward_kernel.py:159-310 (one
 // Triton program per (kv block, query head), dQ/dK/dV accumulated with fp32 atomics) and
