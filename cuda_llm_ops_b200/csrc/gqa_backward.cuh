@@ -78,6 +78,44 @@ enum : int {
     SITE_BWD_DRAIN = 45,
 };
 
+// Epilogue staging.  The 256 element-wise threads hold a 128 x 128 fp32 tile, one row per thread (tensor-memory lane)
+// and 64 of its columns each; stored row by thread, every store instruction would touch 32 rows (measured: 11,000
+// cycles for the 128 KB of one dK/dV block).  So a tile goes through shared memory (free once the last MMA has retired),
+// rows padded by 16 bytes so that both the row-per-thread writes and the row-per-warp reads are conflict-free, and
+// leaves with 512 contiguous bytes per store instruction.
+constexpr int kStageRowF32 = kD * 4 + 16;
+constexpr int kStageRowBf16 = kD * 2 + 16;
+// 32 values of one row, columns [col0, col0 + 32)
+__device__ __forceinline__ void stage_f32(uint8_t* tile, int row, int col0, const float (&v)[32]) {
+    float4* dst = reinterpret_cast<float4*>(tile + row * kStageRowF32 + col0 * 4);
+#pragma unroll
+    for (int e = 0; e < 32; e += 4) dst[e >> 2] = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+}
+__device__ __forceinline__ void stage_bf16(uint8_t* tile, int row, int col0, const float (&v)[32]) {
+    uint4* dst = reinterpret_cast<uint4*>(tile + row * kStageRowBf16 + col0 * 2);
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+        uint4 pkt;
+        pkt.x = pack_bf16x2(v[e + 0], v[e + 1]);
+        pkt.y = pack_bf16x2(v[e + 2], v[e + 3]);
+        pkt.z = pack_bf16x2(v[e + 4], v[e + 5]);
+        pkt.w = pack_bf16x2(v[e + 6], v[e + 7]);
+        dst[e >> 3] = pkt;
+    }
+}
+// The first `rows` rows of a staged tile to `out` (row r at out + r * kD); warp w8 of 8 takes every eighth row (fp32)
+// or every eighth pair of rows (bf16: half a warp per row).
+__device__ __forceinline__ void unstage_f32(const uint8_t* tile, float* out, int rows, int w8, int lane) {
+    for (int r = w8; r < rows; r += 8)
+        *reinterpret_cast<float4*>(out + static_cast<long long>(r) * kD + lane * 4) =
+            *reinterpret_cast<const float4*>(tile + r * kStageRowF32 + lane * 16);
+}
+__device__ __forceinline__ void unstage_bf16(const uint8_t* tile, __nv_bfloat16* out, int rows, int w8, int lane) {
+    for (int r = 2 * w8 + (lane >> 4); r < rows; r += 16)
+        *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * kD + (lane & 15) * 8) =
+            *reinterpret_cast<const uint4*>(tile + r * kStageRowBf16 + (lane & 15) * 16);
+}
+
 struct Params {
     const float* lse;    // [B,Hq,Sq], natural log units (forward output)
     const float* delta;  // [B,Hq,Sq], rowsum(dO o O)
@@ -460,23 +498,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mbar_wait(bars.drain(), 0, abort_flag, SITE_BWD_DRAIN, 1);
         __syncwarp();
         tc_fence_after();
-        __nv_bfloat16* out = p.dq + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + qi) * kD + half * 64;
+        // through shared memory (see stage_f32); every MMA has retired, so the Q tile's place is free
+        uint8_t* tile = gen_base;
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
             float ov[32];
             tmem_ld32_wait(tm_dq + lane_base + half * 64 + cc * 32, ov);
-            if (row_ok) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                    uint4 pkt;
-                    pkt.x = pack_bf16x2(ov[e + 0], ov[e + 1]);
-                    pkt.y = pack_bf16x2(ov[e + 2], ov[e + 3]);
-                    pkt.z = pack_bf16x2(ov[e + 4], ov[e + 5]);
-                    pkt.w = pack_bf16x2(ov[e + 6], ov[e + 7]);
-                    *reinterpret_cast<uint4*>(out + cc * 32 + e) = pkt;
-                }
-            }
+            stage_bf16(tile, row, half * 64 + cc * 32, ov);
         }
+        named_bar_sync(1, 2 * kBM);
+        const int rows_here = p.Sq - q0 < kBM ? p.Sq - q0 : kBM;
+        unstage_bf16(tile, p.dq + ((static_cast<long long>(b) * p.Hq + h) * p.Sq + q0) * kD, rows_here, warp, lane);
         tc_fence_before();
     }
     __syncthreads();
@@ -815,13 +847,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             __syncwarp();
             tc_fence_after();
         }
-        const bool row_ok = kvi < p.Skv;
-        const long long out_off = ((static_cast<long long>(b) * p.Hkv + kvh) * p.Skv + kvi) * kD + half * 64;
+        // both tiles through shared memory (see stage_f32); every MMA has retired, so all of it is free
+        static_assert(2 * kBN * kStageRowF32 <= dkdv::kSmemVec, "the staged tiles must fit below the vectors");
+        const int rows_here = p.Skv - kv0 < kBN ? p.Skv - kv0 : kBN;
+        const long long tile_off = ((static_cast<long long>(b) * p.Hkv + kvh) * p.Skv + kv0) * kD;
         const long long tensor_elems = static_cast<long long>(p.B) * p.Hkv * p.Skv * kD;
+        const bool partial = p.head_splits > 1;  // fp32 partial of this head split; summed by bwd_reduce_kernel
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
-            __nv_bfloat16* out = (which == 0 ? p.dv : p.dk) + out_off;
-            float* part = p.head_splits > 1 ? p.dkv_partial + (split * 2LL + which) * tensor_elems + out_off : nullptr;
+            uint8_t* tile = gen_base + which * (kBN * kStageRowF32);
             const uint32_t src = (which == 0 ? tm_dv : tm_dk) + lane_base + half * 64;
 #pragma unroll 1
             for (int cc = 0; cc < 2; ++cc) {
@@ -832,22 +866,20 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 32; ++e) ov[e] = 0.f;
                 }
-                if (row_ok && part) {  // fp32 partial of this head split; summed by bwd_reduce_kernel
-#pragma unroll
-                    for (int e = 0; e < 32; e += 4)
-                        *reinterpret_cast<float4*>(part + cc * 32 + e) = make_float4(ov[e], ov[e + 1], ov[e + 2], ov[e + 3]);
-                } else if (row_ok) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 pkt;
-                        pkt.x = pack_bf16x2(ov[e + 0], ov[e + 1]);
-                        pkt.y = pack_bf16x2(ov[e + 2], ov[e + 3]);
-                        pkt.z = pack_bf16x2(ov[e + 4], ov[e + 5]);
-                        pkt.w = pack_bf16x2(ov[e + 6], ov[e + 7]);
-                        *reinterpret_cast<uint4*>(out + cc * 32 + e) = pkt;
-                    }
-                }
+                if (partial)
+                    stage_f32(tile, row, half * 64 + cc * 32, ov);
+                else
+                    stage_bf16(tile, row, half * 64 + cc * 32, ov);
             }
+        }
+        named_bar_sync(3, 2 * kBM);
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            const uint8_t* tile = gen_base + which * (kBN * kStageRowF32);
+            if (partial)
+                unstage_f32(tile, p.dkv_partial + (split * 2LL + which) * tensor_elems + tile_off, rows_here, warp, lane);
+            else
+                unstage_bf16(tile, (which == 0 ? p.dv : p.dk) + tile_off, rows_here, warp, lane);
         }
         tc_fence_before();
     }
