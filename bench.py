@@ -464,6 +464,27 @@ def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
         t_end = time.time()
         extra["clock_sampling"] = "timed region + %d untimed repeats of the same step" % reps
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    if wl == "prefill_nc" and not args.profile:
+        # The same kernel with cold inputs but without a flush: eight input sets (272 MB, more than the L2) used in
+        # rotation, steps back to back under one pair of events.  Reported beside the flushed figure, not instead.
+        sets = [(randn_bf16((B, Hq, S, 128)), randn_bf16((B, Hkv, S, 128)), randn_bf16((B, Hkv, S, 128)),
+                 torch.empty_like(q)) for _ in range(8)]
+        rot = lambda i: ops.launch_flash_gqa_forward_bf16_kernel(sets[i % 8][0], sets[i % 8][1], sets[i % 8][2],  # noqa: E731
+                                                                 out=sets[i % 8][3], lse=lse, causal=False)
+        for i in range(8):
+            rot(i)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for i in range(32):
+            rot(i)
+        r1.record()
+        barrier()
+        rot_ms = r0.elapsed_time(r1) / 32
+        extra["rotating_inputs"] = {"ms_per_step": rot_ms, "value_per_gpu": units_per_rank / (rot_ms * 1e-3) / scale_div,
+                                    "unit": unit, "note": "eight input sets (272 MB > 126 MB L2) in rotation, 32 steps "
+                                                          "back to back, no flush; the line's value is the flushed one"}
+        del sets
 
     ms_per_step = total_ms / steps
     value = total_units / (ms_per_step * 1e-3) / scale_div
