@@ -588,7 +588,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int head0 = kvh * p.G + split * heads_here;
     const int n_steps = n_i > 0 ? n_i * heads_here : 0;
 
-    if (threadIdx.x == 0) {
+    const uint32_t sm_k = base, sm_v = base + kTileBytes;
+    auto sm_q = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes; };
+    auto sm_do = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes + kQTileBytes; };
+    // copy thread: position in (head, 64-row query tile) order and the copies of one step
+    int ld_h = head0, ld_i = 0;
+    auto load_step = [&](int st) {
+        const int s = st % dkdv::kStages;
+        const int qrow0 = (i_lo + ld_i) * kBQ;
+        mbar_arrive_expect_tx(bars.stream_full(s), kStageBytes);
+        tma_load_4d(sm_q(s), &tm_q, bars.stream_full(s), 0, qrow0, ld_h, b);
+        tma_load_4d(sm_q(s) + kQHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, ld_h, b);
+        tma_load_4d(sm_do(s), &tm_do, bars.stream_full(s), 0, qrow0, ld_h, b);
+        tma_load_4d(sm_do(s) + kQHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, ld_h, b);
+        if (++ld_i == n_i) {
+            ld_i = 0;
+            ++ld_h;
+        }
+    };
+    if (warp == 8 && lane == 0) {
         mbar_init(bars.fixed_full(), 1);
         for (int s = 0; s < dkdv::kStages; ++s) {
             mbar_init(bars.stream_full(s), 1);
@@ -601,6 +619,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_init(bars.drain(), 1);
         *abort_flag = 0;
         fence_mbar_init();
+        // the first copies start before the block has met at its first barrier (every stage is free)
+        if (n_steps > 0) {
+            mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
+            tma_load_4d(sm_k, &tm_k, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_k + kHalfBytes, &tm_k, bars.fixed_full(), 64, kv0, kvh, b);
+            load_step(0);
+            tma_load_4d(sm_v, &tm_v, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_v + kHalfBytes, &tm_v, bars.fixed_full(), 64, kv0, kvh, b);
+            for (int st = 1; st < dkdv::kStages && st < n_steps; ++st) load_step(st);
+        }
     }
     if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -611,32 +639,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
-    const uint32_t sm_k = base, sm_v = base + kTileBytes;
-    auto sm_q = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes; };
-    auto sm_do = [&](int s) { return base + dkdv::kSmemStream + s * kStageBytes + kQTileBytes; };
 
     if (warp == 8) {
         if (lane == 0 && n_steps > 0) {
-            mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
-            tma_load_4d(sm_k, &tm_k, bars.fixed_full(), 0, kv0, kvh, b);
-            tma_load_4d(sm_k + kHalfBytes, &tm_k, bars.fixed_full(), 64, kv0, kvh, b);
-            tma_load_4d(sm_v, &tm_v, bars.fixed_full(), 0, kv0, kvh, b);
-            tma_load_4d(sm_v + kHalfBytes, &tm_v, bars.fixed_full(), 64, kv0, kvh, b);
-            int h = head0, i = 0;
-            for (int st = 0; st < n_steps; ++st) {
+            for (int st = dkdv::kStages; st < n_steps; ++st) {
                 const int s = st % dkdv::kStages;
                 const uint32_t use = static_cast<uint32_t>(st / dkdv::kStages);
-                const int qrow0 = (i_lo + i) * kBQ;
                 mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, st);
-                mbar_arrive_expect_tx(bars.stream_full(s), kStageBytes);
-                tma_load_4d(sm_q(s), &tm_q, bars.stream_full(s), 0, qrow0, h, b);
-                tma_load_4d(sm_q(s) + kQHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, h, b);
-                tma_load_4d(sm_do(s), &tm_do, bars.stream_full(s), 0, qrow0, h, b);
-                tma_load_4d(sm_do(s) + kQHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, h, b);
-                if (++i == n_i) {
-                    i = 0;
-                    ++h;
-                }
+                load_step(st);
             }
             if (*abort_flag) {
                 for (int st = (n_steps > dkdv::kStages ? n_steps - dkdv::kStages : 0); st < n_steps; ++st) {
