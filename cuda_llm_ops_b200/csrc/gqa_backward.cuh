@@ -220,6 +220,9 @@ struct Bars {
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+    // lets a dependent launch (the dK/dV kernel, which does not read this kernel's output) start filling SMs as soon
+    // as every block of this grid has been scheduled; without such a launch behind it the instruction does nothing
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -1020,8 +1023,23 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     CLLO_CUDA_TRY(cudaGetLastError());
     bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, dq::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
     CLLO_CUDA_TRY(cudaGetLastError());
-    bwd_dkdv_kernel<<<static_cast<unsigned>(blocks_kv), kThreads, dkdv::kSmemBytes, stream>>>(tm_q64, tm_k, tm_v, tm_do64, p);
-    CLLO_CUDA_TRY(cudaGetLastError());
+    // The dK/dV kernel reads nothing that the dQ kernel writes (both need only the delta kernel's output, complete
+    // before the dQ kernel starts), so it is launched with programmatic stream serialisation and never waits on its
+    // predecessor: its blocks move onto the SMs that the last wave of dQ blocks leaves free.  (The dQ kernel signals
+    // at its start; the condition is met once its last block has been scheduled.)
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(blocks_kv));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = dkdv::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, bwd_dkdv_kernel, tm_q64, tm_k, tm_v, tm_do64, p));
+    }
     if (p.head_splits > 1) {
         bwd_reduce_kernel<<<static_cast<unsigned>(blocks_reduce), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,
                                                                             p.dv, p.dk);
