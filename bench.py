@@ -550,7 +550,7 @@ def measure(args, wl, rank, world, local_rank, steps, warmup, light=False):
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                 "kernel": "rope_bf16_kernel" if wl == "rope" else "decode_splitkv_kernel; the divisor is the average time of a whole call over the timed region, "
                           "which also holds the counters' memset and launch gaps" if bound == "hbm"
-                          else ("bwd_delta_kernel + bwd_dq_kernel + bwd_dkdv_kernel (one call)" if wl == "backward"
+                          else ("bwd_delta_kernel + bwd_grads_kernel (dK/dV and dQ blocks in one grid) + bwd_reduce_kernel (one call)" if wl == "backward"
                                 else ("sgqa_fwd_kernel (bound by gathering 512 B per list entry out of L2, mma.sync "
                                       "products; the tensor peak is quoted for scale only)" if wl == "sgqa"
                                       else ("mla_fwd_kernel" if wl == "mla" else

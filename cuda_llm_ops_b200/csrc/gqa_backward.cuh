@@ -1,11 +1,12 @@
-// GQA attention backward for sm_100a (tcgen05 / tensor memory), as two kernels without atomics:
+// GQA attention backward for sm_100a (tcgen05 / tensor memory) without atomics: one grid (bwd_grads_kernel) of two
+// kinds of block,
 //
-//   bwd_dq_kernel     one block per (batch, query head, 128 query rows); loops over KV tiles.
+//   bwd_dq_block      one block per (batch, query head, 128 query rows); loops over KV tiles.
 //                     S = Q K^T and dP = dO V^T into tensor memory; 256 threads turn them into
 //                     dS = P o (dP - D) * scale with P = exp(scale*S - lse) (no row reduction: the forward
 //                     pass left lse, a small pre-pass leaves D = rowsum(dO o O)); dS goes back to tensor
 //                     memory as bf16 (a region of its own, two buffers) and feeds dQ += dS K as the A operand.
-//   bwd_dkdv_kernel   one block per (batch, kv head, 128 kv rows); loops over all query rows of all heads of
+//   bwd_dkdv_block    one block per (batch, kv head, 128 kv rows); loops over all query rows of all heads of
 //                     the group in steps of 64 rows.  It forms the TRANSPOSED tiles directly, S^T = K Q^T and
 //                     dP^T = V dO^T, so that P^T and dS^T are again A operands in tensor memory for
 //                     dV += P^T dO and dK += dS^T Q: no transposes through shared memory, and dK/dV are
@@ -217,12 +218,8 @@ struct Bars {
 };
 }  // namespace dq
 
-__global__ void __launch_bounds__(kThreads, 1)
-bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
-    // lets a dependent launch (the dK/dV kernel, which does not read this kernel's output) start filling SMs as soon
-    // as every block of this grid has been scheduled; without such a launch behind it the instruction does nothing
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+__device__ __forceinline__ void bwd_dq_block(const CUtensorMap* tm_q, const CUtensorMap* tm_k, const CUtensorMap* tm_v,
+                                             const CUtensorMap* tm_do, const Params& p, long long block_id) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -232,7 +229,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // warp index through a shuffle: the compiler then knows it to be the same in every lane
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
-    long long id = blockIdx.x;
+    long long id = block_id;
     const int g = static_cast<int>(id % p.G);
     id /= p.G;
     const int qt = p.n_qt - 1 - static_cast<int>(id % p.n_qt);  // heavy causal tiles first
@@ -258,14 +255,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     auto load_k = [&](int j) {
         const int s = j % dq::kKStages;
         mbar_arrive_expect_tx(bars.k_full(s), kTileBytes);
-        tma_load_4d(sm_k(s), &tm_k, bars.k_full(s), 0, (j_lo + j) * kBN, kvh, b);
-        tma_load_4d(sm_k(s) + kHalfBytes, &tm_k, bars.k_full(s), 64, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_k(s), tm_k, bars.k_full(s), 0, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_k(s) + kHalfBytes, tm_k, bars.k_full(s), 64, (j_lo + j) * kBN, kvh, b);
     };
     auto load_v = [&](int j) {
         const int s = j % dq::kVStages;
         mbar_arrive_expect_tx(bars.v_full(s), kTileBytes);
-        tma_load_4d(sm_v(s), &tm_v, bars.v_full(s), 0, (j_lo + j) * kBN, kvh, b);
-        tma_load_4d(sm_v(s) + kHalfBytes, &tm_v, bars.v_full(s), 64, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_v(s), tm_v, bars.v_full(s), 0, (j_lo + j) * kBN, kvh, b);
+        tma_load_4d(sm_v(s) + kHalfBytes, tm_v, bars.v_full(s), 64, (j_lo + j) * kBN, kvh, b);
     };
 
     if (warp == 8 && lane == 0) {
@@ -286,10 +283,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         fence_mbar_init();
         // the first copies start before the block has met at its first barrier
         mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
-        tma_load_4d(sm_q, &tm_q, bars.fixed_full(), 0, q0, h, b);
-        tma_load_4d(sm_q + kHalfBytes, &tm_q, bars.fixed_full(), 64, q0, h, b);
-        tma_load_4d(sm_do, &tm_do, bars.fixed_full(), 0, q0, h, b);
-        tma_load_4d(sm_do + kHalfBytes, &tm_do, bars.fixed_full(), 64, q0, h, b);
+        tma_load_4d(sm_q, tm_q, bars.fixed_full(), 0, q0, h, b);
+        tma_load_4d(sm_q + kHalfBytes, tm_q, bars.fixed_full(), 64, q0, h, b);
+        tma_load_4d(sm_do, tm_do, bars.fixed_full(), 0, q0, h, b);
+        tma_load_4d(sm_do + kHalfBytes, tm_do, bars.fixed_full(), 64, q0, h, b);
         load_k(0);
         load_v(0);
     }
@@ -558,9 +555,8 @@ struct Bars {
 };
 }  // namespace dkdv
 
-__global__ void __launch_bounds__(kThreads, 1)
-bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+__device__ __forceinline__ void bwd_dkdv_block(const CUtensorMap* tm_q, const CUtensorMap* tm_k, const CUtensorMap* tm_v,
+                                               const CUtensorMap* tm_do, const Params& p, long long block_id) {
     using namespace dkdv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -572,7 +568,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // warp index through a shuffle: the compiler then knows it to be the same in every lane
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
-    long long id = blockIdx.x;
+    long long id = block_id;
     const int split = static_cast<int>(id % p.head_splits);
     id /= p.head_splits;
     const int jt = static_cast<int>(id % p.n_kt);  // early kv tiles carry the most query tiles when causal
@@ -600,10 +596,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int s = st % dkdv::kStages;
         const int qrow0 = (i_lo + ld_i) * kBQ;
         mbar_arrive_expect_tx(bars.stream_full(s), kStageBytes);
-        tma_load_4d(sm_q(s), &tm_q, bars.stream_full(s), 0, qrow0, ld_h, b);
-        tma_load_4d(sm_q(s) + kQHalfBytes, &tm_q, bars.stream_full(s), 64, qrow0, ld_h, b);
-        tma_load_4d(sm_do(s), &tm_do, bars.stream_full(s), 0, qrow0, ld_h, b);
-        tma_load_4d(sm_do(s) + kQHalfBytes, &tm_do, bars.stream_full(s), 64, qrow0, ld_h, b);
+        tma_load_4d(sm_q(s), tm_q, bars.stream_full(s), 0, qrow0, ld_h, b);
+        tma_load_4d(sm_q(s) + kQHalfBytes, tm_q, bars.stream_full(s), 64, qrow0, ld_h, b);
+        tma_load_4d(sm_do(s), tm_do, bars.stream_full(s), 0, qrow0, ld_h, b);
+        tma_load_4d(sm_do(s) + kQHalfBytes, tm_do, bars.stream_full(s), 64, qrow0, ld_h, b);
         if (++ld_i == n_i) {
             ld_i = 0;
             ++ld_h;
@@ -625,11 +621,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // the first copies start before the block has met at its first barrier (every stage is free)
         if (n_steps > 0) {
             mbar_arrive_expect_tx(bars.fixed_full(), 2 * kTileBytes);
-            tma_load_4d(sm_k, &tm_k, bars.fixed_full(), 0, kv0, kvh, b);
-            tma_load_4d(sm_k + kHalfBytes, &tm_k, bars.fixed_full(), 64, kv0, kvh, b);
+            tma_load_4d(sm_k, tm_k, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_k + kHalfBytes, tm_k, bars.fixed_full(), 64, kv0, kvh, b);
             load_step(0);
-            tma_load_4d(sm_v, &tm_v, bars.fixed_full(), 0, kv0, kvh, b);
-            tma_load_4d(sm_v + kHalfBytes, &tm_v, bars.fixed_full(), 64, kv0, kvh, b);
+            tma_load_4d(sm_v, tm_v, bars.fixed_full(), 0, kv0, kvh, b);
+            tma_load_4d(sm_v + kHalfBytes, tm_v, bars.fixed_full(), 64, kv0, kvh, b);
             for (int st = 1; st < dkdv::kStages && st < n_steps; ++st) load_step(st);
         }
     }
@@ -903,6 +899,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
 }
 
+// Both kinds of block in ONE grid: the dK/dV blocks first (they are the longer ones), then the dQ blocks, which move
+// onto the SMs as the last wave of dK/dV blocks drains -- two launches would leave each kernel's last wave to itself
+// (512 equal blocks on 148 SMs: 4 waves where 3.46 would do).  Neither kind reads what the other writes.  Measured
+// against the alternatives (upstream's shape causal / non-causal / B=2, Hq=32, Hkv=4, S=8192 causal, us per call): two
+// launches 273 / 512 / 3858; the second launched with programmatic stream serialisation 272 / 474 / 3900; this grid
+// 278 / 475 / 3470; the two kinds interleaved block by block 380 / 676 / 5060 (an SM that alternates between the two
+// bodies runs both much slower).
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_grads_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ CUtensorMap tm_q64, const __grid_constant__ CUtensorMap tm_do64, const Params p,
+                 const unsigned blocks_kv) {
+    if (blockIdx.x < blocks_kv)
+        bwd_dkdv_block(&tm_q64, &tm_k, &tm_v, &tm_do64, p, blockIdx.x);
+    else
+        bwd_dq_block(&tm_q, &tm_k, &tm_v, &tm_do, p, blockIdx.x - blocks_kv);
+}
+constexpr int kGradsSmemBytes = dq::kSmemBytes > dkdv::kSmemBytes ? dq::kSmemBytes : dkdv::kSmemBytes;
+
 // Sum of the head splits' fp32 partials -> bf16 dV and dK (fixed order: deterministic).  4 elements per thread.
 __global__ void __launch_bounds__(256) bwd_reduce_kernel(const float* __restrict__ partial, int splits,
                                                          long long tensor_elems, __nv_bfloat16* __restrict__ dv,
@@ -999,7 +1014,7 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     // every grid size is checked before the first launch, so a refused call has written nothing
     const long long tensor_elems = static_cast<long long>(B) * Hkv * Skv * kD;
     const long long blocks_reduce = (2 * tensor_elems / 4 + 255) / 256;
-    if (blocks_dq > 0x7fffffffLL || blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL ||
+    if (blocks_dq + blocks_kv > 0x7fffffffLL || (rows + 7) / 8 > 0x7fffffffLL ||
         (p.head_splits > 1 && blocks_reduce > 0x7fffffffLL))
         return CLLO_E_UNSUPPORTED;
 
@@ -1012,34 +1027,16 @@ static int launch(const void* q, const void* k, const void* v, const void* o, co
     if ((rc = prefill::encode_bhsd_map(&tm_do64, grad_o, B, Hq, Sq, dkdv::kBQ)) != CLLO_OK) return rc;
 
     if (!di->backward_attr_set) {
-        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::kSmemBytes));
-        CLLO_CUDA_TRY(
-            cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkdv::kSmemBytes));
+        CLLO_CUDA_TRY(cudaFuncSetAttribute(bwd_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradsSmemBytes));
         di->backward_attr_set = true;
     }
     bwd_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(grad_o), static_cast<float*>(workspace),
         rows);
     CLLO_CUDA_TRY(cudaGetLastError());
-    bwd_dq_kernel<<<static_cast<unsigned>(blocks_dq), kThreads, dq::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, p);
+    bwd_grads_kernel<<<static_cast<unsigned>(blocks_kv + blocks_dq), kThreads, kGradsSmemBytes, stream>>>(
+        tm_q, tm_k, tm_v, tm_do, tm_q64, tm_do64, p, static_cast<unsigned>(blocks_kv));
     CLLO_CUDA_TRY(cudaGetLastError());
-    // The dK/dV kernel reads nothing that the dQ kernel writes (both need only the delta kernel's output, complete
-    // before the dQ kernel starts), so it is launched with programmatic stream serialisation and never waits on its
-    // predecessor: its blocks move onto the SMs that the last wave of dQ blocks leaves free.  (The dQ kernel signals
-    // at its start; the condition is met once its last block has been scheduled.)
-    {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(blocks_kv));
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = dkdv::kSmemBytes;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        CLLO_CUDA_TRY(cudaLaunchKernelEx(&cfg, bwd_dkdv_kernel, tm_q64, tm_k, tm_v, tm_do64, p));
-    }
     if (p.head_splits > 1) {
         bwd_reduce_kernel<<<static_cast<unsigned>(blocks_reduce), 256, 0, stream>>>(p.dkv_partial, p.head_splits, tensor_elems,
                                                                             p.dv, p.dk);
