@@ -644,6 +644,9 @@ __device__ __forceinline__ void bwd_dkdv_block(const CUtensorMap* tm_q, const CU
             for (int st = dkdv::kStages; st < n_steps; ++st) {
                 const int s = st % dkdv::kStages;
                 const uint32_t use = static_cast<uint32_t>(st / dkdv::kStages);
+                // (a barrier of the stage's own: the commit behind S^T of step st - 2 also covers the products that
+                // read this stage, but this thread runs up to two phases of that barrier ahead, which a parity wait
+                // cannot tell apart)
                 mbar_wait(bars.stream_empty(s), (use & 1u) ^ 1u, abort_flag, SITE_BWD_STREAM_EMPTY, st);
                 load_step(st);
             }
