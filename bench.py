@@ -747,6 +747,8 @@ def run_ours(args, rank, world, local_rank):
         for key in ("e2e", "cpu_baseline", "sharded_check"):
             if res.get(key) is not None:
                 entry[key] = res[key]
+        if (res.get("extra") or {}).get("rotating_inputs"):
+            entry["rotating_inputs"] = res["extra"]["rotating_inputs"]
         if wl == "decode_long" and res.get("sharded_check"):
             entry["speedup_over_1_gpu_same_run"] = res["sharded_check"]["single_gpu_us_same_run"] / res["us_per_step"]
         also[wl] = entry
